@@ -1,0 +1,457 @@
+// Mamba2 selective-state update on an MX8 / MX4-held recurrent state, fused in one pass, plus the
+// stand-alone MX codec kernels.  sm_100a.
+//
+// Work decomposition of the fused kernel: one CTA per (batch, head); inside it one lane owns one
+// 16-value block of a row (so block maximum, pair maxima, exponent and micro-exponent bits never
+// leave the thread), dstate/16 neighbouring lanes own one row, and the <h', C> read-out is a
+// shuffle reduction over those lanes.  B and C of the head's group stay in registers for all
+// `dim` rows.  Each lane moves 16 B of mantissas per row with one 128-bit load and one 128-bit
+// store; the next row's loads are issued before the current row is computed.
+//
+// The kernel is bound by instruction issue, not by HBM, on B200: at 18 bytes per block read and
+// written the memory system could deliver one value every ~12 issue slots per SM sub-partition,
+// and decode + update + read-out + exponent + rounding + random bits need more than that.
+#include <algorithm>
+
+#include "lq_mx_codec.cuh"
+
+namespace lq {
+
+constexpr int kUpdateThreads = 128;
+
+// ---- block load / store in either storage layout -----------------------------------------------
+struct MxRaw {
+  uint4 q;        // 16 mantissa bytes (8 for packed MX4: x, y)
+  uint32_t e;     // shared exponent byte
+  uint32_t mic;   // micro-exponent bits, bit i = pair i
+};
+
+template <int BITS, int LAYOUT>
+struct MxBlockIO {
+  static constexpr bool kNibbles = (BITS == 4 && LAYOUT == LQ_MX_LAYOUT_PACKED);
+  static constexpr int kQBytes = kNibbles ? 8 : 16;
+
+  __device__ __forceinline__ static MxRaw load(const lq_mx_state& s, int64_t qrow, int64_t erow, int64_t mrow, int blk) {
+    MxRaw r;
+    const uint8_t* q = static_cast<const uint8_t*>(s.q_state) + qrow + blk * kQBytes;
+    if (kNibbles) {
+      const uint2 v = *reinterpret_cast<const uint2*>(q);
+      r.q = make_uint4(v.x, v.y, 0u, 0u);
+    } else {
+      r.q = *reinterpret_cast<const uint4*>(q);
+    }
+    r.e = s.shared_exp[erow + blk];
+    if (LAYOUT == LQ_MX_LAYOUT_PACKED) {
+      r.mic = s.micro_exp[mrow + blk];
+    } else {
+      const uint2 m = *reinterpret_cast<const uint2*>(s.micro_exp + mrow + blk * 8);
+      r.mic = (((m.x & 0x01010101u) * 0x10204080u) >> 28) | ((((m.y & 0x01010101u) * 0x10204080u) >> 28) << 4);
+    }
+    return r;
+  }
+
+  __device__ __forceinline__ static void codes_of(const MxRaw& r, uint32_t (&codes)[4]) {
+    if (kNibbles) {
+      mx4_nibbles_to_bytes(r.q.x, r.q.y, codes);
+    } else {
+      codes[0] = r.q.x; codes[1] = r.q.y; codes[2] = r.q.z; codes[3] = r.q.w;
+    }
+  }
+
+  __device__ __forceinline__ static void store(const lq_mx_state& s, int64_t qrow, int64_t erow, int64_t mrow, int blk,
+                                               const uint32_t (&codes)[4], uint32_t e, uint32_t mic) {
+    uint8_t* q = static_cast<uint8_t*>(s.q_state) + qrow + blk * kQBytes;
+    if (kNibbles) {
+      uint32_t lo, hi;
+      mx4_bytes_to_nibbles(codes, lo, hi);
+      *reinterpret_cast<uint2*>(q) = make_uint2(lo, hi);
+    } else {
+      *reinterpret_cast<uint4*>(q) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    }
+    s.shared_exp[erow + blk] = static_cast<uint8_t>(e);
+    if (LAYOUT == LQ_MX_LAYOUT_PACKED) {
+      s.micro_exp[mrow + blk] = static_cast<uint8_t>(mic);
+    } else {
+      const uint32_t lo = ((mic & 0xFu) * 0x00204081u) & 0x01010101u;
+      const uint32_t hi = (((mic >> 4) & 0xFu) * 0x00204081u) & 0x01010101u;
+      *reinterpret_cast<uint2*>(s.micro_exp + mrow + blk * 8) = make_uint2(lo, hi);
+    }
+  }
+};
+
+template <int MODE>
+__device__ __forceinline__ MxRoundCtx make_round_ctx(const lq_rounding& r, uint64_t lin) {
+  MxRoundCtx c;
+  c.k0 = static_cast<uint32_t>(r.seed);
+  c.k1 = static_cast<uint32_t>(r.seed >> 32);
+  c.wrap32 = r.rng_offset < (1ull << 32) ? 1u : 0u;
+  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 3) : (r.rng_offset + lin);
+  c.step = static_cast<uint32_t>(r.step);
+  c.layer = r.layer;
+  c.words = (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED16) ? r.words + lin : nullptr;
+  return c;
+}
+
+struct MxUpdateDerived {
+  int32_t nblk;        // dstate / 16
+  int32_t lpr_log2;    // lanes per row = 1 << lpr_log2 >= nblk
+  int32_t dt_uniform;  // dt and dt_bias do not depend on the row (dim) index
+  int32_t a_scalar;    // A depends on the head only
+};
+
+__device__ __forceinline__ float softplus_ref(float x) { return x <= 20.0f ? logf(1.0f + expf(x)) : x; }
+
+template <int BITS, int LAYOUT, int MODE>
+__global__ void __launch_bounds__(kUpdateThreads) mx_state_update_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
+  using IO = MxBlockIO<BITS, LAYOUT>;
+  const lq_mx_state& s = a.state;
+  const int H = s.heads, P = s.dim, N = s.dstate;
+  const int b = blockIdx.x / H;
+  const int h = blockIdx.x - b * H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blk = lane & ((1 << d.lpr_log2) - 1);
+  const int rsub = lane >> d.lpr_log2;
+  const int rows_per_warp = 32 >> d.lpr_log2;
+  const int rows_per_pass = rows_per_warp * (kUpdateThreads / 32);
+  const bool blk_ok = blk < d.nblk;
+  const int n0 = blk * 16;
+  const int grp = h / (H / a.ngroups);
+  const unsigned int* cut = mx_exp_cut_table<BITS>();
+
+  // B and C of this head's group, this lane's 16 columns
+  float Bv[16], Cv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    Bv[i] = blk_ok ? load_as_float(a.B, b * a.B_stride[0] + grp * a.B_stride[1] + (n0 + i) * a.B_stride[2], a.B_dtype) : 0.0f;
+    Cv[i] = blk_ok ? load_as_float(a.C, b * a.C_stride[0] + grp * a.C_stride[1] + (n0 + i) * a.C_stride[2], a.C_dtype) : 0.0f;
+  }
+
+  auto row_dt = [&](int p) {
+    float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1] + p * a.dt_stride[2], a.dt_dtype);
+    if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0] + p * a.dt_bias_stride[1], a.dt_bias_dtype);
+    if (a.dt_softplus) dt = softplus_ref(dt);
+    return dt;
+  };
+  float dt_h = 0.0f, dA_h = 0.0f;
+  if (d.dt_uniform) {
+    dt_h = row_dt(0);
+    if (d.a_scalar) dA_h = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt_h);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) Bv[i] *= dt_h;  // (B * dt), then * x per row: the reference's order
+  }
+
+  const int64_t qbase = b * s.q_stride[0] + h * s.q_stride[1];
+  const int64_t ebase = b * s.exp_stride[0] + h * s.exp_stride[1];
+  const int64_t mbase = b * s.micro_stride[0] + h * s.micro_stride[1];
+
+  int p0 = warp * rows_per_warp;
+  MxRaw cur = {make_uint4(0, 0, 0, 0), 127u, 0u};
+  if (blk_ok && p0 + rsub < P)
+    cur = IO::load(s, qbase + (p0 + rsub) * s.q_stride[2], ebase + (p0 + rsub) * s.exp_stride[2],
+                   mbase + (p0 + rsub) * s.micro_stride[2], blk);
+
+#pragma unroll 1
+  for (; p0 < P; p0 += rows_per_pass) {
+    const int p = p0 + rsub;
+    const bool active = blk_ok && p < P;
+    // issue the next row's loads before working on this one
+    const int pn = p + rows_per_pass;
+    MxRaw nxt = {make_uint4(0, 0, 0, 0), 127u, 0u};
+    if (blk_ok && pn < P)
+      nxt = IO::load(s, qbase + pn * s.q_stride[2], ebase + pn * s.exp_stride[2], mbase + pn * s.micro_stride[2], blk);
+
+    float y = 0.0f;
+    float xv = 0.0f;
+    if (active) {
+      uint32_t codes[4];
+      IO::codes_of(cur, codes);
+      float hv[16];
+      mx_decode_block(codes, cur.e, cur.mic, hv);
+      xv = load_as_float(a.x, b * a.x_stride[0] + h * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
+      if (d.dt_uniform && d.a_scalar) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * xv;
+      } else {
+        const float dt = d.dt_uniform ? dt_h : row_dt(p);
+        const float bscale = d.dt_uniform ? 1.0f : dt;  // Bv already holds B * dt when dt is uniform
+        if (d.a_scalar) {
+          const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + (Bv[i] * bscale) * xv;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
+            hv[i] = hv[i] * expf(Ai * dt) + (Bv[i] * bscale) * xv;
+          }
+        }
+      }
+      float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) {
+        y0 = fmaf(hv[i], Cv[i], y0);
+        y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
+        y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
+        y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
+      }
+      y = (y0 + y1) + (y2 + y3);
+
+      const uint64_t lin = ((static_cast<uint64_t>(b) * H + h) * P + p) * static_cast<uint64_t>(N) + n0;
+      if (a.h_out) {
+        float4* dst = reinterpret_cast<float4*>(a.h_out + lin);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_float4(hv[4 * i], hv[4 * i + 1], hv[4 * i + 2], hv[4 * i + 3]);
+      }
+      const MxRoundCtx ctx = make_round_ctx<MODE>(a.rounding, lin);
+      uint32_t e_new, mic_new;
+      mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e_new, mic_new);
+      IO::store(s, qbase + p * s.q_stride[2], ebase + p * s.exp_stride[2], mbase + p * s.micro_stride[2], blk, codes, e_new,
+                mic_new);
+    }
+    // y = <h', C> over the row: reduce across the lanes that share it
+    for (int o = (1 << d.lpr_log2) >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+    if (active && blk == 0) {
+      if (a.D) y += xv * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
+      if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
+      store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
+    }
+    cur = nxt;
+  }
+}
+
+// ---- stand-alone codec kernels: one thread per 16-value block ----------------------------------
+template <int BITS, int LAYOUT, int MODE>
+__global__ void mx_quantize_kernel(const lq_mx_state s, const void* __restrict__ src, int src_dtype, int64_t src_row_stride,
+                                   const lq_rounding rnd, int64_t total_blocks) {
+  using IO = MxBlockIO<BITS, LAYOUT>;
+  const int nblk = s.dstate / 16;
+  const unsigned int* cut = mx_exp_cut_table<BITS>();
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total_blocks;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = t / nblk;
+    const int blk = static_cast<int>(t - row * nblk);
+    const int p = static_cast<int>(row % s.dim);
+    const int64_t bh = row / s.dim;
+    const int h = static_cast<int>(bh % s.heads);
+    const int64_t b = bh / s.heads;
+    float hv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) hv[i] = load_as_float(src, row * src_row_stride + blk * 16 + i, src_dtype);
+    const uint64_t lin = static_cast<uint64_t>(row) * s.dstate + blk * 16;
+    const MxRoundCtx ctx = make_round_ctx<MODE>(rnd, lin);
+    uint32_t codes[4], e, mic;
+    mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e, mic);
+    IO::store(s, b * s.q_stride[0] + h * s.q_stride[1] + p * s.q_stride[2],
+              b * s.exp_stride[0] + h * s.exp_stride[1] + p * s.exp_stride[2],
+              b * s.micro_stride[0] + h * s.micro_stride[1] + p * s.micro_stride[2], blk, codes, e, mic);
+  }
+}
+
+template <int BITS, int LAYOUT>
+__global__ void mx_dequantize_kernel(const lq_mx_state s, float* __restrict__ dst, int64_t dst_row_stride, int64_t total_blocks) {
+  using IO = MxBlockIO<BITS, LAYOUT>;
+  const int nblk = s.dstate / 16;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total_blocks;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = t / nblk;
+    const int blk = static_cast<int>(t - row * nblk);
+    const int p = static_cast<int>(row % s.dim);
+    const int64_t bh = row / s.dim;
+    const int h = static_cast<int>(bh % s.heads);
+    const int64_t b = bh / s.heads;
+    const MxRaw r = IO::load(s, b * s.q_stride[0] + h * s.q_stride[1] + p * s.q_stride[2],
+                             b * s.exp_stride[0] + h * s.exp_stride[1] + p * s.exp_stride[2],
+                             b * s.micro_stride[0] + h * s.micro_stride[1] + p * s.micro_stride[2], blk);
+    uint32_t codes[4];
+    IO::codes_of(r, codes);
+    float hv[16];
+    mx_decode_block(codes, r.e, r.mic, hv);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dst[row * dst_row_stride + blk * 16 + i] = hv[i];
+  }
+}
+
+template <int BITS, int SRC_LAYOUT, int DST_LAYOUT>
+__global__ void mx_convert_kernel(const lq_mx_state src, const lq_mx_state dst, int64_t total_blocks) {
+  using IOS = MxBlockIO<BITS, SRC_LAYOUT>;
+  using IOD = MxBlockIO<BITS, DST_LAYOUT>;
+  const int nblk = src.dstate / 16;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total_blocks;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = t / nblk;
+    const int blk = static_cast<int>(t - row * nblk);
+    const int p = static_cast<int>(row % src.dim);
+    const int64_t bh = row / src.dim;
+    const int h = static_cast<int>(bh % src.heads);
+    const int64_t b = bh / src.heads;
+    const MxRaw r = IOS::load(src, b * src.q_stride[0] + h * src.q_stride[1] + p * src.q_stride[2],
+                              b * src.exp_stride[0] + h * src.exp_stride[1] + p * src.exp_stride[2],
+                              b * src.micro_stride[0] + h * src.micro_stride[1] + p * src.micro_stride[2], blk);
+    uint32_t codes[4];
+    IOS::codes_of(r, codes);
+    IOD::store(dst, b * dst.q_stride[0] + h * dst.q_stride[1] + p * dst.q_stride[2],
+               b * dst.exp_stride[0] + h * dst.exp_stride[1] + p * dst.exp_stride[2],
+               b * dst.micro_stride[0] + h * dst.micro_stride[1] + p * dst.micro_stride[2], blk, codes, r.e, r.mic);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+static int validate_state(const lq_mx_state& s, const char* who) {
+  LQ_CHECK_ARG(s.q_state && s.shared_exp && s.micro_exp, "%s: null state pointer", who);
+  LQ_CHECK_ARG(s.format_bits == 8 || s.format_bits == 4, "%s: Only MX8 and MX4 state quantization are supported, got format_bits=%d",
+               who, s.format_bits);
+  LQ_CHECK_ARG(s.layout == LQ_MX_LAYOUT_REFERENCE || s.layout == LQ_MX_LAYOUT_PACKED, "%s: unknown layout %d", who, s.layout);
+  LQ_CHECK_ARG(s.batch > 0 && s.heads > 0 && s.dim > 0 && s.dstate > 0, "%s: empty state [%d,%d,%d,%d]", who, s.batch,
+               s.heads, s.dim, s.dstate);
+  LQ_CHECK_ARG(s.dstate % 16 == 0, "%s: MX%d state dim must be divisible by 16, got %d", who, s.format_bits, s.dstate);
+  LQ_CHECK_ARG(static_cast<int64_t>(s.batch) * s.heads < (1ll << 31), "%s: batch*heads too large", who);
+  const bool nib = s.format_bits == 4 && s.layout == LQ_MX_LAYOUT_PACKED;
+  const int qalign = nib ? 8 : 16;
+  LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(s.q_state) % qalign == 0, "%s: q_state must be %d-byte aligned", who, qalign);
+  for (int i = 0; i < 3; ++i)
+    LQ_CHECK_ARG(s.q_stride[i] % qalign == 0, "%s: q_state strides must be multiples of %d bytes", who, qalign);
+  if (s.layout == LQ_MX_LAYOUT_REFERENCE) {
+    LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(s.micro_exp) % 8 == 0, "%s: micro_exp must be 8-byte aligned", who);
+    for (int i = 0; i < 3; ++i) LQ_CHECK_ARG(s.micro_stride[i] % 8 == 0, "%s: micro_exp strides must be multiples of 8", who);
+  }
+  return LQ_OK;
+}
+
+static int validate_rounding(const lq_rounding& r, const char* who) {
+  LQ_CHECK_ARG(r.mode >= LQ_ROUND_HALF_UP && r.mode <= LQ_ROUND_SUPPLIED16, "%s: unknown rounding mode %d", who, r.mode);
+  if (r.mode == LQ_ROUND_SUPPLIED || r.mode == LQ_ROUND_SUPPLIED16) {
+    LQ_CHECK_ARG(r.words != nullptr, "%s: rounding mode %d needs words", who, r.mode);
+    LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(r.words) % 16 == 0, "%s: rounding words must be 16-byte aligned", who);
+  }
+  return LQ_OK;
+}
+
+template <int BITS, int LAYOUT>
+static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived& d, cudaStream_t st) {
+  const dim3 grid(a.state.batch * a.state.heads), block(kUpdateThreads);
+  switch (a.rounding.mode) {
+    case LQ_ROUND_HALF_UP: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, 0, st>>>(a, d); break;
+    case LQ_ROUND_HALF_EVEN: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, 0, st>>>(a, d); break;
+    case LQ_ROUND_PHILOX_REF: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(a, d); break;
+    case LQ_ROUND_SUPPLIED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(a, d); break;
+    case LQ_ROUND_PHILOX_LAYERED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(a, d); break;
+    default: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED16><<<grid, block, 0, st>>>(a, d); break;
+  }
+}
+
+template <int BITS, int LAYOUT>
+static void launch_quantize_mode(const lq_mx_state& s, const void* src, int dt, int64_t stride, const lq_rounding& r,
+                                 int64_t total, cudaStream_t st) {
+  const int block = 128;
+  const int grid = static_cast<int>(std::min<int64_t>((total + block - 1) / block, 1 << 20));
+  switch (r.mode) {
+    case LQ_ROUND_HALF_UP: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    case LQ_ROUND_HALF_EVEN: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    case LQ_ROUND_PHILOX_REF: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    case LQ_ROUND_SUPPLIED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    case LQ_ROUND_PHILOX_LAYERED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    default: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED16><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+  }
+}
+
+#define LQ_DISPATCH_BITS_LAYOUT(bits, layout, CALL)                                   \
+  do {                                                                                \
+    if ((bits) == 8 && (layout) == LQ_MX_LAYOUT_REFERENCE) { CALL(8, LQ_MX_LAYOUT_REFERENCE); } \
+    else if ((bits) == 8) { CALL(8, LQ_MX_LAYOUT_PACKED); }                           \
+    else if ((layout) == LQ_MX_LAYOUT_REFERENCE) { CALL(4, LQ_MX_LAYOUT_REFERENCE); } \
+    else { CALL(4, LQ_MX_LAYOUT_PACKED); }                                            \
+  } while (0)
+
+}  // namespace lq
+
+using namespace lq;
+
+LQ_EXPORT int lq_mx_state_update(const lq_mx_update_args* args, void* cuda_stream) {
+  LQ_CHECK_ARG(args != nullptr, "lq_mx_state_update: null args");
+  const lq_mx_update_args& a = *args;
+  if (int rc = validate_state(a.state, "lq_mx_state_update")) return rc;
+  if (int rc = validate_rounding(a.rounding, "lq_mx_state_update")) return rc;
+  LQ_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C && a.out, "lq_mx_state_update: null operand");
+  LQ_CHECK_ARG(valid_dtype(a.x_dtype) && valid_dtype(a.dt_dtype) && valid_dtype(a.A_dtype) && valid_dtype(a.B_dtype) &&
+                   valid_dtype(a.C_dtype) && valid_dtype(a.out_dtype),
+               "lq_mx_state_update: bad dtype");
+  LQ_CHECK_ARG(!a.dt_bias || valid_dtype(a.dt_bias_dtype), "lq_mx_state_update: bad dt_bias dtype");
+  LQ_CHECK_ARG(!a.D || valid_dtype(a.D_dtype), "lq_mx_state_update: bad D dtype");
+  LQ_CHECK_ARG(!a.z || valid_dtype(a.z_dtype), "lq_mx_state_update: bad z dtype");
+  LQ_CHECK_ARG(a.ngroups > 0 && a.state.heads % a.ngroups == 0, "lq_mx_state_update: heads=%d not divisible by ngroups=%d",
+               a.state.heads, a.ngroups);
+  MxUpdateDerived d;
+  d.nblk = a.state.dstate / 16;
+  if (d.nblk > 32) return fail(LQ_ERR_UNSUPPORTED, "lq_mx_state_update: dstate=%d > 512 is not implemented", a.state.dstate);
+  d.lpr_log2 = 0;
+  while ((1 << d.lpr_log2) < d.nblk) ++d.lpr_log2;
+  d.dt_uniform = (a.dt_stride[2] == 0 && (!a.dt_bias || a.dt_bias_stride[1] == 0)) ? 1 : 0;
+  d.a_scalar = (a.A_stride[1] == 0 && a.A_stride[2] == 0) ? 1 : 0;
+  if (a.h_out) LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(a.h_out) % 16 == 0, "lq_mx_state_update: h_out must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+#define LQ_CALL(B_, L_) launch_update_mode<B_, L_>(a, d, st)
+  LQ_DISPATCH_BITS_LAYOUT(a.state.format_bits, a.state.layout, LQ_CALL);
+#undef LQ_CALL
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+LQ_EXPORT int lq_mx_quantize(const lq_mx_state* state, const void* src, int32_t src_dtype, int64_t src_row_stride,
+                              const lq_rounding* rounding, void* cuda_stream) {
+  LQ_CHECK_ARG(state && src && rounding, "lq_mx_quantize: null argument");
+  if (int rc = validate_state(*state, "lq_mx_quantize")) return rc;
+  if (int rc = validate_rounding(*rounding, "lq_mx_quantize")) return rc;
+  LQ_CHECK_ARG(valid_dtype(src_dtype), "lq_mx_quantize: bad dtype");
+  LQ_CHECK_ARG(src_row_stride >= state->dstate, "lq_mx_quantize: src_row_stride=%lld < dstate", (long long)src_row_stride);
+  const int64_t total = static_cast<int64_t>(state->batch) * state->heads * state->dim * (state->dstate / 16);
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+#define LQ_CALL(B_, L_) launch_quantize_mode<B_, L_>(*state, src, src_dtype, src_row_stride, *rounding, total, st)
+  LQ_DISPATCH_BITS_LAYOUT(state->format_bits, state->layout, LQ_CALL);
+#undef LQ_CALL
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+LQ_EXPORT int lq_mx_dequantize(const lq_mx_state* state, float* dst, int64_t dst_row_stride, void* cuda_stream) {
+  LQ_CHECK_ARG(state && dst, "lq_mx_dequantize: null argument");
+  if (int rc = validate_state(*state, "lq_mx_dequantize")) return rc;
+  LQ_CHECK_ARG(dst_row_stride >= state->dstate, "lq_mx_dequantize: dst_row_stride < dstate");
+  const int64_t total = static_cast<int64_t>(state->batch) * state->heads * state->dim * (state->dstate / 16);
+  const int block = 128;
+  const int grid = static_cast<int>(std::min<int64_t>((total + block - 1) / block, 1 << 20));
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+#define LQ_CALL(B_, L_) mx_dequantize_kernel<B_, L_><<<grid, block, 0, st>>>(*state, dst, dst_row_stride, total)
+  LQ_DISPATCH_BITS_LAYOUT(state->format_bits, state->layout, LQ_CALL);
+#undef LQ_CALL
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+LQ_EXPORT int lq_mx_convert_layout(const lq_mx_state* src, const lq_mx_state* dst, void* cuda_stream) {
+  LQ_CHECK_ARG(src && dst, "lq_mx_convert_layout: null argument");
+  if (int rc = validate_state(*src, "lq_mx_convert_layout(src)")) return rc;
+  if (int rc = validate_state(*dst, "lq_mx_convert_layout(dst)")) return rc;
+  LQ_CHECK_ARG(src->format_bits == dst->format_bits && src->batch == dst->batch && src->heads == dst->heads &&
+                   src->dim == dst->dim && src->dstate == dst->dstate,
+               "lq_mx_convert_layout: source and destination differ in shape or format");
+  const int64_t total = static_cast<int64_t>(src->batch) * src->heads * src->dim * (src->dstate / 16);
+  const int block = 128;
+  const int grid = static_cast<int>(std::min<int64_t>((total + block - 1) / block, 1 << 20));
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const int bits = src->format_bits;
+#define LQ_CONV(B_, S_, D_) mx_convert_kernel<B_, S_, D_><<<grid, block, 0, st>>>(*src, *dst, total)
+  if (bits == 8) {
+    if (src->layout == LQ_MX_LAYOUT_REFERENCE && dst->layout == LQ_MX_LAYOUT_PACKED) LQ_CONV(8, LQ_MX_LAYOUT_REFERENCE, LQ_MX_LAYOUT_PACKED);
+    else if (src->layout == LQ_MX_LAYOUT_PACKED && dst->layout == LQ_MX_LAYOUT_REFERENCE) LQ_CONV(8, LQ_MX_LAYOUT_PACKED, LQ_MX_LAYOUT_REFERENCE);
+    else if (src->layout == LQ_MX_LAYOUT_PACKED) LQ_CONV(8, LQ_MX_LAYOUT_PACKED, LQ_MX_LAYOUT_PACKED);
+    else LQ_CONV(8, LQ_MX_LAYOUT_REFERENCE, LQ_MX_LAYOUT_REFERENCE);
+  } else {
+    if (src->layout == LQ_MX_LAYOUT_REFERENCE && dst->layout == LQ_MX_LAYOUT_PACKED) LQ_CONV(4, LQ_MX_LAYOUT_REFERENCE, LQ_MX_LAYOUT_PACKED);
+    else if (src->layout == LQ_MX_LAYOUT_PACKED && dst->layout == LQ_MX_LAYOUT_REFERENCE) LQ_CONV(4, LQ_MX_LAYOUT_PACKED, LQ_MX_LAYOUT_REFERENCE);
+    else if (src->layout == LQ_MX_LAYOUT_PACKED) LQ_CONV(4, LQ_MX_LAYOUT_PACKED, LQ_MX_LAYOUT_PACKED);
+    else LQ_CONV(4, LQ_MX_LAYOUT_REFERENCE, LQ_MX_LAYOUT_REFERENCE);
+  }
+#undef LQ_CONV
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
