@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot paths on B200: one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload (BASELINE config 1, the configuration the metric is quoted on): the fused Mamba2
+MX8 state update at batch 8 per GPU, 128 heads x 64 x 128 state, 8 B/C groups, stochastic
+rounding, for the 24 Mamba2 layers of one Nemotron-H-8B decode step.  One "step" = those 24
+per-layer launches over 24 distinct layer states (453 MB of packed state per step, larger than
+the 126 MB L2, so no launch finds its state cached from the previous step).
+
+  value     algorithmic GB/s over all ranks, operands resident in HBM (18 B per 16-value block,
+            read + written)
+  e2e       the same metric through the public Python call (mx_state_selective_update) with the
+            step's x / dt / B / C copied from pinned host memory and y copied back, all inside
+            the timed region
+  roofline  the MX8 update kernel against the measured HBM copy bandwidth
+  sweep     larger shapes of the same kernels (MX8 / MX4 at batch 256, INT4-KV decode attention
+            cells), each as algorithmic GB/s and fraction of the measured peak
+
+Ranks shard the batch (weak scaling: batch 8 per GPU) and exchange nothing on the hot path;
+torch.distributed carries only the barrier and the max-over-ranks of the timings.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HEADS, DIM, DSTATE, GROUPS, LAYERS = 128, 64, 128, 8, 24
+MX8_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 18 * 2  # 2,359,296
+MX4_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 10 * 2  # 1,310,720
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def attn_bytes(batch: int, ctx: int, gs: int = 32, hkv: int = 8, hq: int = 32, d: int = 128) -> int:
+    row = d // 2 * 2 + 2 * 4 * (d // gs)  # K + V codes and scales of one token of one kv head
+    return batch * (hkv * ctx * row + hkv * row + 2 * hkv * d * 2 + 2 * hq * d * 2)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 200 ms while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            self.result = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args, rank: int, world: int) -> int:
+    """The reference's CPU path for this workload on the box's host cores.  The reference has no CPU
+    code for the fused update itself, so this is the oracle's numpy restatement of its kernel."""
+    if rank != 0:
+        return 0
+    import oracle.timing as ot
+    cores = os.cpu_count() or 1
+    batch = 8
+    for _ in range(max(args.warmup, 0) and 1):
+        ot.time_mx_update(batch, 8, threads=cores)
+    times = []
+    for _ in range(max(1, min(args.steps, 5))):
+        sec, used, nbytes = ot.time_mx_update(batch, 8, threads=cores)
+        times.append(sec)
+    sec = sum(times) / len(times)
+    value = nbytes / sec / 1e9
+    sample = f"one of the step's 24 layers (batch {batch}, {nbytes} algorithmic bytes) per timed step, {len(times)} steps"
+    line = {
+        "impl": "reference", "metric": "mx8_state_update_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": 1 if args.warmup else 0, "ms_per_step": sec * 1e3 * LAYERS, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus, batch),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "ms_per_step extrapolates the sampled layer to the 24-layer step",
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> dict:
+    return {
+        "workload": "BASELINE config 1: Mamba2 MX8 state update, one Nemotron-H-8B decode step = 24 layers",
+        "batch_per_gpu": batch_per_gpu, "global_batch": batch_per_gpu * n_gpus, "heads": HEADS, "head_dim": DIM, "d_state": DSTATE,
+        "bc_groups": GROUPS, "layers_per_step": LAYERS, "state_format": "MX8 packed (18 B / 16-value block)",
+        "rounding": f"stochastic, Philox4x32-10, {rng} stream, seed 0", "parallelism": f"batch-sharded dp{n_gpus}, no collective",
+        "l2": "24 distinct layer states per step (453 MB per GPU) exceed the 126 MB L2; no flush needed",
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch-per-gpu", type=int, default=8)
+    ap.add_argument("--rng", default="reference", choices=["reference", "layered"],
+                    help="random stream of the headline number (both are always reported)")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return reference_arm(args, rank, world)
+
+    import numpy as np
+    import torch
+    from layer_quant_b200 import int4_8b_attention as ia
+    from layer_quant_b200 import mamba_state_8b_kernel as mk
+    from layer_quant_b200 import sharding
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl ours needs a CUDA device (there is no CPU path)")
+    rank, local_rank, world = sharding.init_from_env()
+    dev = torch.device("cuda", local_rank)
+    B = args.batch_per_gpu
+    peak, peak_src = hbm_peak()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def randn(*shape, dtype=torch.bfloat16):
+        return torch.randn(shape, generator=gen, device=dev, dtype=torch.float32).to(dtype)
+
+    # ---- per-layer states and operands (config 1 distributions) -------------------------------------
+    def make_layers(batch, n_layers, bits):
+        layers = []
+        for li in range(n_layers):
+            cache = mk.allocate_state_kernel_cache(randn(batch, HEADS, DIM, DSTATE, dtype=torch.float32) * 0.5, 16, bits)
+            cache.layer = li
+            ops = dict(
+                x=randn(batch, HEADS, DIM), dt=randn(batch, HEADS)[:, :, None].expand(batch, HEADS, DIM),
+                A=(-torch.exp(torch.rand(HEADS, generator=gen, device=dev) * float(np.log(16.0))))[:, None, None].expand(HEADS, DIM, DSTATE),
+                B=randn(batch, GROUPS, DSTATE), C=randn(batch, GROUPS, DSTATE),
+                D=torch.rand(HEADS, generator=gen, device=dev)[:, None].expand(HEADS, DIM),
+                dt_bias=(torch.rand(HEADS, generator=gen, device=dev) * 2.0 - 4.0)[:, None].expand(HEADS, DIM),
+                out=torch.empty((batch, HEADS, DIM), device=dev, dtype=torch.bfloat16))
+            layers.append((cache, ops))
+        return layers
+
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)  # device-side decode-step counter read by the kernels
+
+    def make_step(layers, stream_name, graph=True):
+        """The decode step's state updates as one replayable unit: 24 prepared launches plus the
+        one-thread counter bump, captured in a CUDA graph (as a serving loop would replay it)."""
+        plans = [mk.MxUpdatePlan(cache, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True,
+                                 stochastic=True, seed=0, rng_stream=stream_name, out=o["out"], step_counter=counter)
+                 for cache, o in layers]
+
+        def eager():
+            for p in plans:
+                p.run()
+            mk.advance_step_counter(counter)
+
+        if not graph:
+            return eager
+        eager()
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            eager()
+        g._plans = plans
+        return g.replay
+
+    def timed(fn, steps, warmup):
+        """Max-over-ranks seconds for `steps` calls of fn, CUDA events on the launching stream."""
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize(dev)
+        sharding.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        sharding.barrier()
+        return sharding.all_reduce_max(e0.elapsed_time(e1) / 1e3, dev)
+
+    layers8 = make_layers(B, LAYERS, 8)
+    bytes_step = MX8_BYTES_PER_SEQ_LAYER * B * LAYERS
+
+    results = {}
+    with ClockSampler(local_rank) as clocks:
+        for name in ("reference", "layered"):
+            results[name] = timed(make_step(layers8, name), args.steps, args.warmup)
+    eager_sec = timed(make_step(layers8, args.rng, graph=False), args.steps, args.warmup)
+    sec = results[args.rng]
+    value = bytes_step * world * args.steps / sec / 1e9
+    ms_per_step = sec / args.steps * 1e3
+    per_launch_s = sec / (args.steps * LAYERS)
+    achieved = MX8_BYTES_PER_SEQ_LAYER * B / per_launch_s / 1e9
+
+    # ---- end to end: host buffers in, host buffer out, through the public call ------------------------
+    host_in = []
+    for cache, o in layers8:
+        host_in.append({k: torch.empty(s, dtype=torch.bfloat16).pin_memory()
+                        for k, s in (("x", (B, HEADS, DIM)), ("dt", (B, HEADS)), ("B", (B, GROUPS, DSTATE)), ("C", (B, GROUPS, DSTATE)))})
+        for k, v in host_in[-1].items():
+            v.copy_(torch.randn(v.shape).to(torch.bfloat16))
+    host_out = [torch.empty((B, HEADS, DIM), dtype=torch.bfloat16).pin_memory() for _ in layers8]
+    dev_in = [{k: torch.empty_like(v, device=dev) for k, v in h.items()} for h in host_in]
+    h2d = sum(v.numel() * v.element_size() for v in host_in[0].values()) * LAYERS
+    d2h = host_out[0].numel() * host_out[0].element_size() * LAYERS
+
+    def e2e_step():
+        for (cache, o), hi, di, ho in zip(layers8, host_in, dev_in, host_out):
+            for k in hi:
+                di[k].copy_(hi[k], non_blocking=True)
+            y = mk.mx_state_selective_update(cache, di["x"], di["dt"][:, :, None].expand(B, HEADS, DIM), o["A"], di["B"], di["C"],
+                                             D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True, stochastic=True, seed=0,
+                                             rng_stream=args.rng)
+            ho.copy_(y, non_blocking=True)
+
+    sec_e2e = timed(e2e_step, args.steps, args.warmup)
+    e2e_value = bytes_step * world * args.steps / sec_e2e / 1e9
+
+    # ---- sweep: the larger shapes of the same kernels -----------------------------------------------------
+    sweep = {}
+    if not args.no_sweep:
+        del layers8
+        torch.cuda.empty_cache()
+        for bits, per_seq in ((8, MX8_BYTES_PER_SEQ_LAYER), (4, MX4_BYTES_PER_SEQ_LAYER)):
+            big = make_layers(256, 4, bits)
+            for name in ("reference", "layered"):
+                s = timed(make_step(big, name), 5, 3)
+                gbs = per_seq * 256 * 4 * 5 / s / 1e9
+                sweep[f"mx{bits}_update_b256_{name}_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                               "us_per_launch": round(s / 20 * 1e6, 1)}
+            del big
+            torch.cuda.empty_cache()
+        for (bb, ctx) in ((1, 1024), (16, 8192), (64, 32768), (256, 8192)):
+            cap = ctx
+            reps = max(1, int(np.ceil(4 * 126e6 / attn_bytes(bb, ctx))))  # distinct caches: >= 4x L2 in rotation
+            reps = min(reps, 64)
+            caches = []
+            for _ in range(reps):
+                c = ia._allocate_layer_cache(bb, 8, cap, 128, 4, dev)
+                c.k_packed.copy_(torch.randint(0, 256, c.k_packed.shape, generator=gen, device=dev, dtype=torch.int16).to(torch.uint8))
+                c.v_packed.copy_(torch.randint(0, 256, c.v_packed.shape, generator=gen, device=dev, dtype=torch.int16).to(torch.uint8))
+                c.k_scale.copy_(torch.rand(c.k_scale.shape, generator=gen, device=dev) * 0.4 + 0.1)
+                c.v_scale.copy_(torch.rand(c.v_scale.shape, generator=gen, device=dev) * 0.4 + 0.1)
+                caches.append(c)
+            q = randn(bb, 32, 1, 128)
+            kn, vn = randn(bb, 8, 1, 128), randn(bb, 8, 1, 128)
+
+            def attn_step():
+                for c in caches:
+                    ia._append_decode_attention(q, kn, vn, c, ctx, 4, 32)
+
+            s = timed(attn_step, 5, 3)
+            gbs = attn_bytes(bb, ctx) * reps * 5 / s / 1e9
+            sweep[f"int4_attn_b{bb}_ctx{ctx}"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                  "us_per_launch": round(s / (5 * reps) * 1e6, 1)}
+            del caches
+            torch.cuda.empty_cache()
+
+    # ---- CPU baseline (rank 0, bounded sample) ----------------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle.timing as ot
+        csec, cores, nbytes = ot.time_mx_update(8, 8, threads=os.cpu_count() or 1)
+        cpu = {"value": nbytes / csec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+               "sample": "one layer of the step (batch 8, 18.9 MB algorithmic), numpy restatement of the reference kernel, one run"}
+
+    if rank == 0:
+        line = {
+            "metric": "mx8_state_update_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(world, B, args.rng),
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": sec_e2e / args.steps * 1e3},
+            "gpu_launches": args.steps * (LAYERS + 1),
+            "launch_mode": "24 update launches + 1 counter bump per step, replayed from a CUDA graph",
+            "eager_launch": {"GBps": bytes_step * world * args.steps / eager_sec / 1e9, "ms_per_step": eager_sec / args.steps * 1e3},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "mx_state_update_kernel<8, packed, philox>",
+                         "algorithmic_bytes_per_launch": MX8_BYTES_PER_SEQ_LAYER * B, "us_per_launch": per_launch_s * 1e6},
+            "cpu_baseline": cpu,
+            "clocks": clocks.result,
+            "streams": {k: {"GBps": bytes_step * world * args.steps / v / 1e9, "ms_per_step": v / args.steps * 1e3} for k, v in results.items()},
+            "sweep": sweep,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

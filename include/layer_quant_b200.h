@@ -90,6 +90,10 @@ typedef struct lq_rounding {
   uint64_t step;         /* PHILOX_LAYERED: counter word; PHILOX_REF: unused (see rng_offset)    */
   uint64_t rng_offset;   /* PHILOX_REF: RNG_OFFSET = step * numel of the reference (:659, :716)  */
   const uint32_t* words; /* SUPPLIED / SUPPLIED16: device, one word per value, [B,H,P,N] dense   */
+  const uint64_t* step_counter; /* optional device counter read when the kernel runs: its value is
+                            added to `step`, and value * numel(state) to `rng_offset`, so that a
+                            launch recorded once (CUDA graph) draws fresh numbers on every replay;
+                            advance it with lq_counter_add                                        */
 } lq_rounding;
 
 /* One decode step of the Mamba2 selective-state update on an MX-held state, fused:
@@ -127,6 +131,9 @@ int lq_mx_quantize(const lq_mx_state* state, const void* src, int32_t src_dtype,
 
 /* q * 2^(shared_exp - 127 + micro) -> dense fp32 [rows, dstate] (mamba_state_8b_kernel.py:132). */
 int lq_mx_dequantize(const lq_mx_state* state, float* dst, int64_t dst_row_stride, void* cuda_stream);
+
+/* *counter += inc on the stream (one thread); pairs with lq_rounding.step_counter. */
+int lq_counter_add(uint64_t* counter, uint64_t inc, void* cuda_stream);
 
 /* Convert between the two storage layouts (same format_bits and shape in both). */
 int lq_mx_convert_layout(const lq_mx_state* src, const lq_mx_state* dst, void* cuda_stream);

@@ -41,7 +41,7 @@ class MxState(C.Structure):
 class Rounding(C.Structure):
     _fields_ = [
         ("mode", C.c_int32), ("layer", C.c_uint32), ("seed", C.c_uint64), ("step", C.c_uint64),
-        ("rng_offset", C.c_uint64), ("words", C.c_void_p),
+        ("rng_offset", C.c_uint64), ("words", C.c_void_p), ("step_counter", C.c_void_p),
     ]
 
 
@@ -100,6 +100,7 @@ def lib() -> C.CDLL:
     l.lq_mx_state_update.argtypes = [C.POINTER(MxUpdateArgs), C.c_void_p]
     l.lq_mx_quantize.argtypes = [C.POINTER(MxState), C.c_void_p, C.c_int32, C.c_int64, C.POINTER(Rounding), C.c_void_p]
     l.lq_mx_dequantize.argtypes = [C.POINTER(MxState), C.c_void_p, C.c_int64, C.c_void_p]
+    l.lq_counter_add.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     l.lq_mx_convert_layout.argtypes = [C.POINTER(MxState), C.POINTER(MxState), C.c_void_p]
     l.lq_int4_kv_append.argtypes = [C.POINTER(Int4Cache), C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                                     C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]

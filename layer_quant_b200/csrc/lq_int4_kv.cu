@@ -561,7 +561,7 @@ static int pick_splits(int batch, int kv_heads, int ctx_len) {
     const int64_t waves = (ctas + sms - 1) / sms;
     double score = static_cast<double>(ctas) / static_cast<double>(waves * sms);  // how full the last wave is
     score *= static_cast<double>(tps) / (tps + 2.0);  // a CTA pays ~2 tiles of ramp-up and merge
-    if (score > best_score + 1e-9) {
+    if (score > best_score * 1.02) {  // more splits only when they clearly pay: each adds merge traffic
       best_score = score;
       best = s;
     }

@@ -79,14 +79,17 @@ struct MxBlockIO {
   }
 };
 
+// `numel` = values in the whole state: the reference advances its Philox offset by it every step.
 template <int MODE>
-__device__ __forceinline__ MxRoundCtx make_round_ctx(const lq_rounding& r, uint64_t lin) {
+__device__ __forceinline__ MxRoundCtx make_round_ctx(const lq_rounding& r, uint64_t lin, uint64_t numel) {
   MxRoundCtx c;
   c.k0 = static_cast<uint32_t>(r.seed);
   c.k1 = static_cast<uint32_t>(r.seed >> 32);
-  c.wrap32 = r.rng_offset < (1ull << 32) ? 1u : 0u;
-  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 3) : (r.rng_offset + lin);
-  c.step = static_cast<uint32_t>(r.step);
+  const uint64_t extra = r.step_counter ? __ldg(reinterpret_cast<const unsigned long long*>(r.step_counter)) : 0ull;
+  const uint64_t rng_offset = r.rng_offset + extra * numel;
+  c.wrap32 = rng_offset < (1ull << 32) ? 1u : 0u;
+  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 3) : (rng_offset + lin);
+  c.step = static_cast<uint32_t>(r.step + extra);
   c.layer = r.layer;
   c.words = (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED16) ? r.words + lin : nullptr;
   return c;
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(kUpdateThreads) mx_state_update_kernel(const l
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_float4(hv[4 * i], hv[4 * i + 1], hv[4 * i + 2], hv[4 * i + 3]);
       }
-      const MxRoundCtx ctx = make_round_ctx<MODE>(a.rounding, lin);
+      const MxRoundCtx ctx = make_round_ctx<MODE>(a.rounding, lin, static_cast<uint64_t>(s.batch) * H * P * N);
       uint32_t e_new, mic_new;
       mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e_new, mic_new);
       IO::store(s, qbase + p * s.q_stride[2], ebase + p * s.exp_stride[2], mbase + p * s.micro_stride[2], blk, codes, e_new,
@@ -238,7 +241,7 @@ __global__ void mx_quantize_kernel(const lq_mx_state s, const void* __restrict__
 #pragma unroll
     for (int i = 0; i < 16; ++i) hv[i] = load_as_float(src, row * src_row_stride + blk * 16 + i, src_dtype);
     const uint64_t lin = static_cast<uint64_t>(row) * s.dstate + blk * 16;
-    const MxRoundCtx ctx = make_round_ctx<MODE>(rnd, lin);
+    const MxRoundCtx ctx = make_round_ctx<MODE>(rnd, lin, static_cast<uint64_t>(s.batch) * s.heads * s.dim * s.dstate);
     uint32_t codes[4], e, mic;
     mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e, mic);
     IO::store(s, b * s.q_stride[0] + h * s.q_stride[1] + p * s.q_stride[2],
@@ -295,6 +298,8 @@ __global__ void mx_convert_kernel(const lq_mx_state src, const lq_mx_state dst, 
   }
 }
 
+__global__ void counter_add_kernel(unsigned long long* counter, unsigned long long inc) { *counter += inc; }
+
 // ---- host side --------------------------------------------------------------------------------
 static int validate_state(const lq_mx_state& s, const char* who) {
   LQ_CHECK_ARG(s.q_state && s.shared_exp && s.micro_exp, "%s: null state pointer", who);
@@ -323,6 +328,7 @@ static int validate_rounding(const lq_rounding& r, const char* who) {
     LQ_CHECK_ARG(r.words != nullptr, "%s: rounding mode %d needs words", who, r.mode);
     LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(r.words) % 16 == 0, "%s: rounding words must be 16-byte aligned", who);
   }
+  LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(r.step_counter) % 8 == 0, "%s: step_counter must be 8-byte aligned", who);
   return LQ_OK;
 }
 
@@ -408,6 +414,13 @@ LQ_EXPORT int lq_mx_quantize(const lq_mx_state* state, const void* src, int32_t 
 #define LQ_CALL(B_, L_) launch_quantize_mode<B_, L_>(*state, src, src_dtype, src_row_stride, *rounding, total, st)
   LQ_DISPATCH_BITS_LAYOUT(state->format_bits, state->layout, LQ_CALL);
 #undef LQ_CALL
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+LQ_EXPORT int lq_counter_add(uint64_t* counter, uint64_t inc, void* cuda_stream) {
+  LQ_CHECK_ARG(counter != nullptr && reinterpret_cast<uintptr_t>(counter) % 8 == 0, "lq_counter_add: counter must be an 8-byte aligned device pointer");
+  counter_add_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(reinterpret_cast<unsigned long long*>(counter), inc);
   LQ_CHECK_CUDA(cudaGetLastError());
   return LQ_OK;
 }

@@ -185,6 +185,104 @@ def allocate_state_kernel_cache(ssm_state_4d: torch.Tensor, group_size: int = MX
     return MambaStateKernelCache(q_state=q, shared_exp=e, micro_exp=m, format_bits=format_bits, layout=layout)
 
 
+class MxUpdatePlan:
+    """A prepared ``mx_state_selective_update`` call: shapes are checked and the argument block of
+    the C entry point is filled once, so that repeating the step costs one ctypes call.  The
+    tensors handed in must stay alive and in place (the plan keeps references).
+
+    ``step_counter`` (a 1-element int64 CUDA tensor) makes the launch replayable from a CUDA
+    graph: the kernel adds its current value to the step when it runs; advance it with
+    :func:`advance_step_counter` at the end of the captured step.  Without it the host-side
+    ``cache.step`` is used and advanced on every :meth:`run`."""
+
+    def __init__(self, cache, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False, stochastic=True,
+                 seed=1234, *, rng_stream=None, rand_words=None, h_out=None, out=None, step_counter=None):
+        if cache.q_state.ndim != 4:
+            raise ValueError(f"Expected q_state [B,H,P,N], got {tuple(cache.q_state.shape)}")
+        batch, nheads, dim, dstate = cache.state_shape
+        if x.shape != (batch, nheads, dim):
+            raise ValueError(f"Expected x shape {(batch, nheads, dim)}, got {tuple(x.shape)}")
+        if B.ndim != 3 or C.ndim != 3:
+            raise ValueError("Expected B and C with shape [batch, ngroups, dstate] for decode update.")
+        if cache.format_bits not in (8, 4):
+            raise ValueError(f"Unsupported MX state format_bits={cache.format_bits}")
+        if dt.ndim != 3 or A.ndim != 3:
+            raise ValueError("Expected dt [batch, heads, dim] and A [heads, dim, dstate] (expanded views are fine).")
+        if D is not None and D.ndim != 2:
+            raise ValueError("Expected D [heads, dim].")
+        if z is not None and z.ndim != 3:
+            raise ValueError("Expected z [batch, heads, dim].")
+        self.device = _lib.require_cuda(cache.q_state, x, dt, A, B, C, D, z, dt_bias, rand_words, h_out, out, step_counter)
+        self.cache = cache
+        self.out = torch.empty_like(x) if out is None else out
+        self._keep = (x, dt, A, B, C, D, z, dt_bias, rand_words, h_out, step_counter)
+        self.numel = batch * nheads * dim * dstate
+        a = self.args = _lib.MxUpdateArgs()
+        a.state = _state_struct(cache)
+        _lib.set_ptr_strides(a, "x", x, 3)
+        _lib.set_ptr_strides(a, "dt", dt, 3)
+        _lib.set_ptr_strides(a, "A", A, 3)
+        _lib.set_ptr_strides(a, "B", B, 3)
+        _lib.set_ptr_strides(a, "C", C, 3)
+        _lib.set_ptr_strides(a, "D", D, 2)
+        _lib.set_ptr_strides(a, "z", z, 3)
+        _lib.set_ptr_strides(a, "out", self.out, 3)
+        if dt_bias is not None:
+            a.dt_bias = dt_bias.data_ptr()
+            a.dt_bias_dtype = _lib.dtype_code(dt_bias)
+            d_strides = D.stride() if D is not None else (0, 0)  # the reference indexes dt_bias with D's strides
+            a.dt_bias_stride[0], a.dt_bias_stride[1] = d_strides[0], d_strides[1]
+        a.ngroups = B.shape[1]
+        a.dt_softplus = 1 if dt_softplus else 0
+        stream = rng_stream or RNG_STREAM
+        r = a.rounding
+        r.seed = _seed_u64(seed)
+        r.layer = int(cache.layer) & 0xFFFFFFFF
+        if rand_words is not None:
+            if (tuple(rand_words.shape) != (batch, nheads, dim, dstate) or rand_words.element_size() != 4
+                    or not rand_words.is_contiguous()):
+                raise ValueError(f"rand_words must be a contiguous 32-bit tensor of shape {(batch, nheads, dim, dstate)}")
+            r.words = rand_words.data_ptr()
+            r.mode = _lib.LQ_ROUND_SUPPLIED16 if stream == "layered" else _lib.LQ_ROUND_SUPPLIED
+        elif not stochastic:
+            r.mode = _lib.LQ_ROUND_HALF_UP
+        elif stream == "reference":
+            r.mode = _lib.LQ_ROUND_PHILOX_REF
+        elif stream == "layered":
+            r.mode = _lib.LQ_ROUND_PHILOX_LAYERED
+        else:
+            raise ValueError(f"unknown rng_stream {stream!r}")
+        if h_out is not None:
+            if tuple(h_out.shape) != (batch, nheads, dim, dstate) or h_out.dtype != torch.float32 or not h_out.is_contiguous():
+                raise ValueError(f"h_out must be contiguous float32 of shape {(batch, nheads, dim, dstate)}")
+            a.h_out = h_out.data_ptr()
+        if step_counter is not None:
+            if step_counter.dtype != torch.int64 or step_counter.numel() != 1:
+                raise ValueError("step_counter must be a 1-element int64 CUDA tensor")
+            r.step_counter = step_counter.data_ptr()
+        self._fn = _lib.lib().lq_mx_state_update
+        self._ref = ct.byref(a)
+
+    def run(self) -> torch.Tensor:
+        r = self.args.rounding
+        step = int(self.cache.step)
+        r.step = step
+        r.rng_offset = (step * self.numel) & 0xFFFFFFFFFFFFFFFF
+        rc = self._fn(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            _lib.check(rc)
+        if not r.step_counter:
+            self.cache.step = step + 1
+        return self.out
+
+
+def advance_step_counter(step_counter: torch.Tensor, inc: int = 1) -> None:
+    """``step_counter += inc`` on the current stream with the library's own one-thread kernel
+    (capturable in a CUDA graph together with the update launches that read the counter)."""
+    dev = _lib.require_cuda(step_counter)
+    _lib.check(_lib.lib().lq_counter_add(step_counter.data_ptr(), int(inc), _lib.stream_ptr(dev)))
+
+
 def mx_state_selective_update(
     cache: MambaStateKernelCache,
     x: torch.Tensor,
@@ -213,70 +311,11 @@ def mx_state_selective_update(
 
     Extras (keyword-only, not in the reference): ``rng_stream`` overrides ``RNG_STREAM``;
     ``rand_words`` (uint32/int32 [B,H,P,N]) supplies the random bits instead of Philox;
-    ``h_out`` (fp32 [B,H,P,N]) receives the updated state before requantisation."""
-    if cache.q_state.ndim != 4:
-        raise ValueError(f"Expected q_state [B,H,P,N], got {tuple(cache.q_state.shape)}")
-    batch, nheads, dim, dstate = cache.state_shape
-    if x.shape != (batch, nheads, dim):
-        raise ValueError(f"Expected x shape {(batch, nheads, dim)}, got {tuple(x.shape)}")
-    if B.ndim != 3 or C.ndim != 3:
-        raise ValueError("Expected B and C with shape [batch, ngroups, dstate] for decode update.")
-    if cache.format_bits not in (8, 4):
-        raise ValueError(f"Unsupported MX state format_bits={cache.format_bits}")
-    if dt.ndim != 3 or A.ndim != 3:
-        raise ValueError("Expected dt [batch, heads, dim] and A [heads, dim, dstate] (expanded views are fine).")
-    if D is not None and D.ndim != 2:
-        raise ValueError("Expected D [heads, dim].")
-    if z is not None and z.ndim != 3:
-        raise ValueError("Expected z [batch, heads, dim].")
-    dev = _lib.require_cuda(cache.q_state, x, dt, A, B, C, D, z, dt_bias, rand_words, h_out, out)
-    if out is None:
-        out = torch.empty_like(x)
-
-    a = _lib.MxUpdateArgs()
-    a.state = _state_struct(cache)
-    _lib.set_ptr_strides(a, "x", x, 3)
-    _lib.set_ptr_strides(a, "dt", dt, 3)
-    _lib.set_ptr_strides(a, "A", A, 3)
-    _lib.set_ptr_strides(a, "B", B, 3)
-    _lib.set_ptr_strides(a, "C", C, 3)
-    _lib.set_ptr_strides(a, "D", D, 2)
-    _lib.set_ptr_strides(a, "z", z, 3)
-    _lib.set_ptr_strides(a, "out", out, 3)
-    if dt_bias is not None:
-        a.dt_bias = dt_bias.data_ptr()
-        a.dt_bias_dtype = _lib.dtype_code(dt_bias)
-        d_strides = D.stride() if D is not None else (0, 0)  # the reference indexes dt_bias with D's strides
-        a.dt_bias_stride[0], a.dt_bias_stride[1] = d_strides[0], d_strides[1]
-    a.ngroups = B.shape[1]
-    a.dt_softplus = 1 if dt_softplus else 0
-    numel = batch * nheads * dim * dstate
-    stream = rng_stream or RNG_STREAM
-    r = a.rounding
-    r.seed = _seed_u64(seed)
-    r.layer = int(cache.layer) & 0xFFFFFFFF
-    r.step = int(cache.step)
-    r.rng_offset = (int(cache.step) * numel) & 0xFFFFFFFFFFFFFFFF
-    if rand_words is not None:
-        if tuple(rand_words.shape) != (batch, nheads, dim, dstate) or rand_words.element_size() != 4 or not rand_words.is_contiguous():
-            raise ValueError(f"rand_words must be a contiguous 32-bit tensor of shape {(batch, nheads, dim, dstate)}")
-        r.words = rand_words.data_ptr()
-        r.mode = _lib.LQ_ROUND_SUPPLIED16 if stream == "layered" else _lib.LQ_ROUND_SUPPLIED
-    elif not stochastic:
-        r.mode = _lib.LQ_ROUND_HALF_UP
-    elif stream == "reference":
-        r.mode = _lib.LQ_ROUND_PHILOX_REF
-    elif stream == "layered":
-        r.mode = _lib.LQ_ROUND_PHILOX_LAYERED
-    else:
-        raise ValueError(f"unknown rng_stream {stream!r}")
-    if h_out is not None:
-        if tuple(h_out.shape) != (batch, nheads, dim, dstate) or h_out.dtype != torch.float32 or not h_out.is_contiguous():
-            raise ValueError(f"h_out must be contiguous float32 of shape {(batch, nheads, dim, dstate)}")
-        a.h_out = h_out.data_ptr()
-    _lib.check(_lib.lib().lq_mx_state_update(ct.byref(a), _lib.stream_ptr(dev)))
-    cache.step += 1
-    return out
+    ``h_out`` (fp32 [B,H,P,N]) receives the updated state before requantisation; ``out`` is
+    written instead of a fresh tensor.  :class:`MxUpdatePlan` prepares the same call once for
+    loops that repeat it."""
+    return MxUpdatePlan(cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus, stochastic=stochastic,
+                        seed=seed, rng_stream=rng_stream, rand_words=rand_words, h_out=h_out, out=out).run()
 
 
 def mx8_state_selective_update(*args, **kwargs) -> torch.Tensor:

@@ -1,0 +1,250 @@
+"""GPU parity of the packed INT4 KV cache: append (quantise + pack) bit-exact against the oracle
+codec, decode attention within 2e-3 relative of the float64 oracle and of the reference kernel's
+own fp32 outputs (golden fixtures), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import bf16r, dev, rel_err, t
+
+pytestmark = pytest.mark.gpu
+
+OUT_RTOL = 2e-3  # relative to the largest output magnitude
+
+
+def ia():
+    from layer_quant_b200 import int4_8b_attention as m
+    return m
+
+
+def make_kv(seed, b, hkv, tlen, d=128, outliers=True):
+    rng = np.random.default_rng(seed)
+    k = rng.standard_normal((b, hkv, tlen, d)).astype(np.float32)
+    v = rng.standard_normal((b, hkv, tlen, d)).astype(np.float32)
+    if outliers:  # 1 % of entries at 8 sigma, the sweep's value distribution
+        k = np.where(rng.random(k.shape) < 0.01, 8.0 * np.sign(k), k)
+        v = np.where(rng.random(v.shape) < 0.01, 8.0 * np.sign(v), v)
+    return bf16r(k), bf16r(v)
+
+
+def fill_cache(m, k, v, gs, capacity=None, dtype=torch.bfloat16):
+    b, hkv, tlen, d = k.shape
+    cap = capacity or max(16, 1 << int(np.ceil(np.log2(max(tlen, 1)))))
+    cache = m._allocate_layer_cache(b, hkv, cap, d, d // gs, dev())
+    for x in (cache.k_packed, cache.v_packed):
+        x.fill_(0x99)
+    for x in (cache.k_scale, cache.v_scale):
+        x.fill_(float("nan"))  # rows beyond seq_len must never be read
+    if tlen:
+        m._pack_kv_into_cache(cache, t(k, dtype), t(v, dtype), torch.arange(tlen, device=dev()), gs)
+    return cache
+
+
+def cache_np(cache):
+    return (cache.k_packed.cpu().numpy(), cache.v_packed.cpu().numpy(), cache.k_scale.cpu().numpy(), cache.v_scale.cpu().numpy())
+
+
+@pytest.mark.parametrize("gs", [16, 32, 64, 128, 8, 2, 6])
+def test_append_bit_exact(gs, golden_dir):
+    m = ia()
+    d = 96 if gs == 6 else 128
+    k, v = make_kv(1, 2, 3, 37, d)
+    if d == 128:  # the rows the reference's fake-quant was pinned on
+        x = np.load(golden_dir / "int4_codec.npz")["codec_x"]
+        k[:2, :2, :5] = x[:2, :, :5][:, :2]
+    k[0, 0, 0, :gs] = 0.0  # an all-zero group: scale floors at 1e-8
+    cache = fill_cache(m, k, v, gs, dtype=torch.float32)
+    assert cache.length == 37
+    kp, vp, ks, vs = cache_np(cache)
+    for src, packed, scale in ((k, kp, ks), (v, vp, vs)):
+        q, s = oracle.int4_encode(src, gs)
+        assert np.array_equal(packed[:, :, :37], oracle.int4_pack_nibbles(q))
+        assert np.array_equal(scale[:, :, :37], s)
+    assert (kp[:, :, 37:] == 0x99).all()
+
+
+def test_append_strided_bf16_and_positions():
+    m = ia()
+    k, v = make_kv(2, 2, 8, 5)
+    # [B, q_len, H, D] storage viewed as [B, H, q_len, D]: what the projection + transpose yields
+    kt = t(k, torch.bfloat16).transpose(1, 2).contiguous().transpose(1, 2)
+    vt = t(v, torch.bfloat16).transpose(1, 2).contiguous().transpose(1, 2)
+    assert not kt.is_contiguous()
+    cache = m._allocate_layer_cache(2, 8, 64, 128, 4, dev())
+    cache.k_packed.zero_(); cache.v_packed.zero_(); cache.k_scale.zero_(); cache.v_scale.zero_()
+    pos = torch.tensor([40, 3, 17, 63, 0], device=dev())
+    m._pack_kv_into_cache(cache, kt, vt, pos, 32)
+    assert cache.length == 64
+    kp, vp, ks, vs = cache_np(cache)
+    q, s = oracle.int4_encode(k, 32)
+    for i, p in enumerate(pos.tolist()):
+        assert np.array_equal(kp[:, :, p], oracle.int4_pack_nibbles(q[:, :, i])) and np.array_equal(ks[:, :, p], s[:, :, i])
+    untouched = sorted(set(range(64)) - set(pos.tolist()))
+    assert (kp[:, :, untouched] == 0).all() and (vs[:, :, untouched] == 0).all()
+
+
+@pytest.mark.parametrize("name", ["t1", "t63", "t64", "t65", "t200_mask", "t130_bool"])
+def test_decode_against_reference_fixtures(golden_dir, name):
+    """Same packed cache, same query: the reference kernel's fp32 output."""
+    m = ia()
+    g = np.load(golden_dir / f"attn_{name}.npz")
+    b, hq, hkv, tlen, gs = (int(v) for v in g["meta"])
+    cache = m.Int4KVLayerCache(t(g["k_packed"]), t(g["v_packed"]), t(g["k_scale"]), t(g["v_scale"]), length=tlen)
+    mask = t(g["mask"]) if "mask" in g else None
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, OUT_RTOL)):
+        for splits in (0, 1, 3):
+            out = m._decode_attention(t(g["q"], dtype), cache, tlen, hq // hkv, gs, attention_mask=mask, splits=splits)
+            assert out.dtype == dtype and out.shape == (b, hq, 128)
+            assert rel_err(out.float().cpu().numpy(), g["out"]) < tol, (dtype, splits)
+    # append path reproduces the fixture's cache rows from its bf16 K/V
+    built = fill_cache(m, g["k"], g["v"], gs)
+    assert torch.equal(built.k_packed[:, :, :tlen], cache.k_packed[:, :, :tlen]) and torch.equal(built.v_scale[:, :, :tlen], cache.v_scale[:, :, :tlen])
+
+
+@pytest.mark.parametrize("tlen", [1, 2, 17, 63, 64, 65, 127, 128, 129, 1000, 1024, 4097])
+def test_decode_context_lengths_and_splits(tlen):
+    m = ia()
+    b, hq, hkv, gs = 2, 32, 8, 32
+    k, v = make_kv(tlen, b, hkv, tlen)
+    q = bf16r(np.random.default_rng(tlen + 1).standard_normal((b, hq, 1, 128)))
+    cache = fill_cache(m, k, v, gs)
+    ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(cache), tlen, gs)
+    ntiles = (tlen + 63) // 64
+    for splits in sorted({0, 1, 2, ntiles, 5}):
+        out = m._decode_attention(t(q, torch.bfloat16), cache, tlen, 4, gs, splits=splits)
+        assert rel_err(out.float().cpu().numpy(), ref) < OUT_RTOL, splits
+        out32 = m._decode_attention(t(q), cache, tlen, 4, gs, splits=splits)
+        assert rel_err(out32.cpu().numpy(), ref) < 2e-5, splits
+    from layer_quant_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+def test_config0_shape_against_reference_cpu_path():
+    """BASELINE config 0: batch 1, 32 query / 8 kv heads, head_dim 128, context 1024, group 32, bf16
+    N(0,1) from seed 0.  Compared with the reference's PyTorch path (fake-quantised K/V + softmax
+    attention) evaluated in float64."""
+    m = ia()
+    gen = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 32, 1, 128, generator=gen).bfloat16()
+    k = torch.randn(1, 8, 1024, 128, generator=gen).bfloat16()
+    v = torch.randn(1, 8, 1024, 128, generator=gen).bfloat16()
+    cache = fill_cache(m, k.float().numpy(), v.float().numpy(), 32)
+    out = m._decode_attention(q.to(dev()), cache, 1024, 4, 32)
+    kd = m.int4_quant_dequant(k, 32).double().repeat_interleave(4, dim=1)
+    vd = m.int4_quant_dequant(v, 32).double().repeat_interleave(4, dim=1)
+    p = torch.softmax(q.double() @ kd.transpose(-1, -2) / 128 ** 0.5, dim=-1)
+    ref = (p @ vd)[:, :, 0].numpy()
+    assert out.shape == (1, 32, 128) and out.dtype == torch.bfloat16
+    assert rel_err(out.float().cpu().numpy(), ref) < OUT_RTOL
+
+
+@pytest.mark.parametrize("gs,ratio", [(16, 4), (64, 4), (128, 2), (32, 1), (32, 2), (64, 8)])
+def test_decode_group_sizes_and_gqa_ratios(gs, ratio):
+    m = ia()
+    b, hkv, tlen = 3, 2, 333
+    k, v = make_kv(7, b, hkv, tlen)
+    q = bf16r(np.random.default_rng(8).standard_normal((b, hkv * ratio, 1, 128)) * 2.0)
+    cache = fill_cache(m, k, v, gs)
+    ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(cache), tlen, gs)
+    out = m._decode_attention(t(q), cache, tlen, ratio, gs, splits=2)
+    assert rel_err(out.cpu().numpy(), ref) < 2e-5
+
+
+def test_decode_masks():
+    m = ia()
+    b, hq, hkv, tlen, gs = 2, 8, 2, 300, 32
+    k, v = make_kv(9, b, hkv, tlen)
+    q = bf16r(np.random.default_rng(10).standard_normal((b, hq, 1, 128)))
+    cache = fill_cache(m, k, v, gs)
+    add = np.zeros((b, 1, 1, tlen), np.float32)
+    add[:, :, :, 100:180] = -np.inf
+    add[1, :, :, 7] = -3.25
+    add[0, :, :, 0:64] = -np.inf  # a fully masked first tile (the reference returns NaN there)
+    keep2d = np.ones((b, tlen + 5), np.int64)
+    keep2d[0, 20:90] = 0
+    short = np.zeros((b, 1, 1, 250), np.float32)  # shorter than the context: the tail is masked out
+    for mask in (add, keep2d, short, add[:, :, :, :].astype(bool) == 0):
+        bias = oracle.decode_attention_mask(mask, b, tlen)
+        ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(cache), tlen, gs, bias)
+        for splits in (1, 4):
+            out = m._decode_attention(t(q), cache, tlen, 4, gs, attention_mask=torch.from_numpy(mask).to(dev()), splits=splits)
+            assert rel_err(out.cpu().numpy(), ref) < 2e-5
+    with pytest.raises(ValueError, match="2D or 4D"):
+        m._decode_attention(t(q), cache, tlen, 4, gs, attention_mask=torch.zeros(3, device=dev()))
+
+
+def test_fused_append_equals_append_then_decode():
+    m = ia()
+    b, hq, hkv, gs = 4, 32, 8, 32
+    for tlen in (1, 2, 64, 65, 129, 700):
+        k, v = make_kv(tlen + 100, b, hkv, tlen)
+        q = bf16r(np.random.default_rng(tlen).standard_normal((b, hq, 1, 128)))
+        cap = 1024
+        two = fill_cache(m, k, v, gs, capacity=cap)
+        one = fill_cache(m, k[:, :, : tlen - 1], v[:, :, : tlen - 1], gs, capacity=cap) if tlen > 1 else fill_cache(m, k[:, :, :0], v[:, :, :0], gs, capacity=cap)
+        ref_out = m._decode_attention(t(q, torch.bfloat16), two, tlen, 4, gs, splits=2)
+        # new token as the strided view a projection + transpose produces
+        kn = t(k[:, :, tlen - 1:], torch.bfloat16).transpose(1, 2).contiguous().transpose(1, 2)
+        vn = t(v[:, :, tlen - 1:], torch.bfloat16).transpose(1, 2).contiguous().transpose(1, 2)
+        for splits in (0, 3):
+            one.k_packed[:, :, tlen - 1] = 0
+            out = m._append_decode_attention(t(q, torch.bfloat16), kn, vn, one, tlen, 4, gs, splits=splits)
+            assert one.length == tlen
+            for name in ("k_packed", "v_packed", "k_scale", "v_scale"):
+                assert torch.equal(getattr(one, name)[:, :, :tlen], getattr(two, name)[:, :, :tlen]), (tlen, name)
+            assert rel_err(out.float().cpu().numpy(), ref_out.float().cpu().numpy()) < 1e-2 * OUT_RTOL + 2 ** -8
+        ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(two), tlen, gs)
+        assert rel_err(out.float().cpu().numpy(), ref) < OUT_RTOL
+
+
+def test_sweep_cell_property_constant_values():
+    """Size-independent property at a sweep cell (batch 64, context 32k, 2.7 GB of cache): when every
+    V row of a head is the same vector, attention returns that vector whatever K and q are."""
+    m = ia()
+    b, hq, hkv, tlen, gs = 64, 32, 8, 32768, 32
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    cache = m._allocate_layer_cache(b, hkv, tlen, 128, 4, dev())
+    cache.k_packed.copy_(torch.randint(0, 256, cache.k_packed.shape, generator=gen, device=dev(), dtype=torch.int16).to(torch.uint8))
+    cache.k_scale.copy_(torch.rand(cache.k_scale.shape, generator=gen, device=dev()) * 0.5 + 0.1)
+    row_codes = torch.randint(0, 256, (b, hkv, 1, 64), generator=gen, device=dev(), dtype=torch.int16).to(torch.uint8)
+    row_scale = torch.rand((b, hkv, 1, 4), generator=gen, device=dev()) + 0.5
+    cache.v_packed.copy_(row_codes.expand_as(cache.v_packed))
+    cache.v_scale.copy_(row_scale.expand_as(cache.v_scale))
+    q = torch.randn((b, hq, 1, 128), generator=gen, device=dev()).bfloat16()
+    out = m._decode_attention(q.float(), cache, tlen, 4, gs)
+    want = oracle.int4_decode(oracle.int4_unpack_nibbles(row_codes.cpu().numpy()), row_scale.cpu().numpy(), gs)[:, :, 0]
+    want = np.repeat(want, 4, axis=1)
+    assert rel_err(out.cpu().numpy(), want) < 1e-4
+    # permuting the context must not change the result (softmax is permutation invariant)
+    perm = torch.randperm(tlen, generator=gen, device=dev())
+    cache2 = m.Int4KVLayerCache(cache.k_packed[:, :, perm].contiguous(), cache.v_packed, cache.k_scale[:, :, perm].contiguous(), cache.v_scale, tlen)
+    out2 = m._decode_attention(q.float(), cache2, tlen, 4, gs)
+    assert rel_err(out2.cpu().numpy(), out.cpu().numpy()) < 1e-4
+
+
+def test_cache_growth_and_errors():
+    m = ia()
+
+    class Holder:
+        pass
+
+    pkv = Holder()
+    c1 = m._ensure_layer_cache(pkv, 7, 2, 8, 5, 128, 32, dev())
+    assert c1.k_packed.shape == (2, 8, 16, 64) and c1.k_scale.shape == (2, 8, 16, 4)
+    k, v = make_kv(3, 2, 8, 16)
+    m._pack_kv_into_cache(c1, t(k, torch.bfloat16), t(v, torch.bfloat16), torch.arange(16, device=dev()), 32)
+    c2 = m._ensure_layer_cache(pkv, 7, 2, 8, 17, 128, 32, dev())
+    assert c2 is not c1 and c2.k_packed.shape[2] == 32 and c2.length == 16
+    assert torch.equal(c2.k_packed[:, :, :16], c1.k_packed) and torch.equal(c2.v_scale[:, :, :16], c1.v_scale)
+    assert m._ensure_layer_cache(pkv, 7, 2, 8, 32, 128, 32, dev()) is c2
+    with pytest.raises(ValueError, match="does not match batch/kv_heads"):
+        m._ensure_layer_cache(pkv, 7, 3, 8, 4, 128, 32, dev())
+    q = torch.zeros((2, 32, 2, 128), device=dev(), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="expects q_len=1"):
+        m._decode_attention(q, c2, 16, 4, 32)
+    with pytest.raises(ValueError, match="seq_len=40 outside"):
+        m._decode_attention(q[:, :, :1], c2, 40, 4, 32)
+    with pytest.raises(NotImplementedError, match="head_dim=64"):
+        c64 = m._allocate_layer_cache(1, 2, 16, 64, 2, dev())
+        m._decode_attention(torch.zeros((1, 8, 1, 64), device=dev()), c64, 4, 4, 32)
