@@ -153,6 +153,10 @@ def main() -> int:
     ap.add_argument("--rng", default="reference", choices=["reference", "layered"],
                     help="random stream of the headline number (both are always reported)")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn"],
+                    help="run only one small kernel case (for ncu captures): plain launches, no graph, no sweep")
+    ap.add_argument("--case-batch", type=int, default=64)
+    ap.add_argument("--case-ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -233,6 +237,30 @@ def main() -> int:
         torch.cuda.synchronize(dev)
         sharding.barrier()
         return sharding.all_reduce_max(e0.elapsed_time(e1) / 1e3, dev)
+
+    if args.case:
+        # one kernel, a few plain launches on a working set larger than L2 and at most a few GB
+        cb = args.case_batch
+        if args.case == "attn":
+            ctx = args.case_ctx
+            c = ia._allocate_layer_cache(cb, 8, ctx, 128, 4, dev)
+            for tns in (c.k_packed, c.v_packed):
+                tns.copy_(torch.randint(0, 256, tns.shape, generator=gen, device=dev, dtype=torch.int16).to(torch.uint8))
+            for tns in (c.k_scale, c.v_scale):
+                tns.copy_(torch.rand(tns.shape, generator=gen, device=dev) * 0.4 + 0.1)
+            q, kn, vn = randn(cb, 32, 1, 128), randn(cb, 8, 1, 128), randn(cb, 8, 1, 128)
+            fn = lambda: ia._append_decode_attention(q, kn, vn, c, ctx, 4, 32)
+            nbytes = attn_bytes(cb, ctx)
+        else:
+            bits = 8 if args.case == "mx8" else 4
+            lay = make_layers(cb, 1, bits)
+            fn = make_step(lay, args.rng, graph=False)
+            nbytes = (MX8_BYTES_PER_SEQ_LAYER if bits == 8 else MX4_BYTES_PER_SEQ_LAYER) * cb
+        sec = timed(fn, args.steps, args.warmup)
+        print(json.dumps({"case": args.case, "batch": cb, "ctx": args.case_ctx if args.case == "attn" else None, "rng": args.rng,
+                          "us_per_launch": sec / args.steps * 1e6, "GBps": nbytes * args.steps / sec / 1e9,
+                          "frac_of_hbm_peak": nbytes * args.steps / sec / 1e9 / peak}), flush=True)
+        return 0
 
     layers8 = make_layers(B, LAYERS, 8)
     bytes_step = MX8_BYTES_PER_SEQ_LAYER * B * LAYERS

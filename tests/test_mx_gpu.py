@@ -2,8 +2,8 @@
 
 Bar: codecs bit-exact (codes, exponents, micro-exponents) against the reference's own outputs
 (golden fixtures) and against the oracle on the same inputs and the same random numbers; SSM
-outputs within 2e-3 relative (relative to the largest output magnitude; bf16 rounding of the
-stored output alone is 2**-9 ~ 1.95e-3 of an element)."""
+outputs: fp32 within 1e-4 of the largest magnitude (the 2e-3 bar with margin), bf16 equal to the
+rounded oracle value up to one bf16 ulp (tests.util.assert_out_close)."""
 import glob
 from pathlib import Path
 
@@ -12,11 +12,10 @@ import pytest
 import torch
 
 import oracle
-from tests.util import (cache_to_numpy, dev, expand_update_operands, make_update_case, oracle_update_operands, rel_err, t)
+from tests.util import (assert_out_close, cache_to_numpy, dev, expand_update_operands, make_update_case, oracle_update_operands, rel_err, t)
 
 pytestmark = pytest.mark.gpu
 
-Y_RTOL = 2e-3
 
 
 def mk():
@@ -123,7 +122,7 @@ def run_update(m, d, bits, layout, stochastic=True, seed=0, steps=1, io_dtype=to
         y = m.mx_state_selective_update(cache, x, dt, A, B, C, D=D, z=z, dt_bias=bias, dt_softplus=softplus,
                                         stochastic=stochastic, seed=seed, rng_stream=rng_stream, h_out=h_out, **kw)
         torch.cuda.synchronize()
-        outs.append((y.float().cpu().numpy(), h_out.cpu().numpy(), *cache_to_numpy(cache)))
+        outs.append((y, h_out.cpu().numpy(), *cache_to_numpy(cache)))
     return cache, outs
 
 
@@ -141,7 +140,7 @@ def test_fused_update_against_reference_fixtures(path, layout):
     assert cache.step == steps
     total = mism = 0
     for s, (y, h, q, e, mi) in enumerate(outs):
-        assert rel_err(y, g[f"y{s}"]) < 2e-5, f"step {s}"
+        assert_out_close(y, g[f"y{s}"])
         # the kernel's codec is bit-exact on the state the kernel itself computed
         numel = h.size
         rnd = oracle.tl_rand(seed, oracle.reference_rng_offsets(s, h.shape)) if stoch else None
@@ -171,8 +170,8 @@ def test_fused_update_config1_shape_against_oracle(bits, layout):
     for s, (y, h, qk, ek, mk_) in enumerate(outs):
         yo, qo, eo, mo, ho = oracle.mx_state_update(q, e, mi, dt_softplus=True, format_bits=bits, rounding="stochastic",
                                                     seed=0, step=s, return_state=True, **ops)
-        assert rel_err(y, yo) < Y_RTOL, f"step {s}: y rel err {rel_err(y, yo)}"
-        np.testing.assert_allclose(h, ho, rtol=1e-5, atol=1e-6)
+        assert_out_close(y, yo)
+        np.testing.assert_allclose(h, ho, rtol=1e-4, atol=1e-6)
         rnd = oracle.tl_rand(0, oracle.reference_rng_offsets(s, h.shape))
         qs, es, ms = oracle.mx_encode(h, mmax, "stochastic", rnd)
         assert np.array_equal(qk, qs) and np.array_equal(ek, es) and np.array_equal(mk_, ms)
@@ -200,7 +199,7 @@ def test_fused_update_shapes_and_supplied_bits(case, bits):
         y, hh, q, e, mi = outs[0]
         q0, e0, m0 = oracle.mx_encode(d["state"], mmax, "half_even")
         yo, *_ = oracle.mx_state_update(q0, e0, m0, dt_softplus=True, format_bits=bits, rounding="half_up", **oracle_update_operands(d))
-        assert rel_err(y, yo) < 2e-5
+        assert_out_close(y, yo)
         if stream == "reference":
             qo, eo, mo = oracle.mx_encode(hh, mmax, "stochastic", oracle.words_to_uniform(words[0]))
         else:
@@ -226,8 +225,8 @@ def test_fused_update_general_operands():
     ops["dt"], ops["A"] = dt_full, A_full
     yo, qo, eo, mo, ho = oracle.mx_state_update(q0, e0, m0, dt_softplus=True, rounding="half_up", return_state=True, **ops)
     assert y.dtype == torch.float16
-    assert rel_err(y.float().cpu().numpy(), yo) < Y_RTOL
-    np.testing.assert_allclose(h_out.cpu().numpy(), ho, rtol=1e-5, atol=1e-6)
+    assert_out_close(y, yo)
+    np.testing.assert_allclose(h_out.cpu().numpy(), ho, rtol=1e-4, atol=1e-6)
     q, e, mi = cache_to_numpy(cache)
     qs, es, ms = oracle.mx_encode(h_out.cpu().numpy(), 63, "half_up")
     assert np.array_equal(q, qs) and np.array_equal(e, es) and np.array_equal(mi, ms)
@@ -266,7 +265,7 @@ def test_full_size_identity_step_is_idempotent(bits):
     # read-out on a slice against torch
     hs = cache.dequantize()[:2]
     yo = torch.einsum("bhpn,bhn->bhp", hs, C[:2].float().repeat_interleave(h // g, dim=1))
-    assert rel_err(y[:2].float().cpu().numpy(), yo.cpu().numpy()) < Y_RTOL
+    assert_out_close(y[:2], yo.cpu().numpy())
 
 
 def test_layered_stream_is_unbiased_and_keyed():

@@ -73,3 +73,19 @@ def rel_err(a, ref):
     a = np.asarray(a, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     return float(np.abs(a - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def assert_out_close(out, ref, fp32_tol=1e-4):
+    """Kernel output (torch tensor) against the float64 oracle.  fp32 outputs: within ``fp32_tol`` of
+    the largest magnitude (the 2e-3 bar with a 20x margin).  bf16 / fp16 outputs carry the
+    rounding of the store itself (half an ulp = 2**-8 / 2**-11 relative, already above 2e-3 for
+    bf16), so they must equal the correctly rounded oracle value up to one ulp of the output type."""
+    ref = np.asarray(ref, dtype=np.float64)
+    got = out.float().cpu().numpy().astype(np.float64)
+    scale = max(np.abs(ref).max(), 1e-30)
+    if out.dtype == torch.float32:
+        assert np.abs(got - ref).max() <= fp32_tol * scale, f"rel err {np.abs(got - ref).max() / scale:.3e}"
+        return
+    ulp = 2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10
+    bad = np.abs(got - ref) > ulp * np.abs(ref) + fp32_tol * scale
+    assert not bad.any(), f"{bad.sum()} outputs off by more than one ulp of {out.dtype}; worst {np.abs(got - ref).max() / scale:.3e} of max"
