@@ -60,16 +60,17 @@ extern "C" {
  *   PHILOX_REF      floor(a) + (u < a - floor(a)), u = tl.rand(seed, rng_offset + linear index):
  *                   the reference's stream, one Philox4x32-10 block per value (:196-199,:659)
  *   SUPPLIED        same rule, u derived from caller-supplied 32-bit words (one per value)
- *   PHILOX_LAYERED  library stream keyed on (seed, layer, step, value index): one Philox4x32-10
- *                   block per 8 values, 16 bits per value, fixed-point rule
- *                   q = ((fix16(v/scale + 64) + r16) >> 16) - 64.  No reference counterpart.
- *   SUPPLIED16      the fixed-point rule with r16 = low 16 bits of caller-supplied words        */
+ *   PHILOX_LAYERED  library stream keyed on (seed, layer, step, block index): one Philox4x32-10
+ *                   block (counter = block index lo/hi, step, layer) per 16-value MX block, value i
+ *                   takes byte i & 3 of word i >> 2 as an 8-bit uniform draw r8; fixed-point rule
+ *                   q = floor(fl32(v/scale + 49152 + r8/256)) - 49152.  No reference counterpart.
+ *   SUPPLIED_FIXED  the fixed-point rule with r8 = low 8 bits of caller-supplied words           */
 #define LQ_ROUND_HALF_UP 0
 #define LQ_ROUND_HALF_EVEN 1
 #define LQ_ROUND_PHILOX_REF 2
 #define LQ_ROUND_SUPPLIED 3
 #define LQ_ROUND_PHILOX_LAYERED 4
-#define LQ_ROUND_SUPPLIED16 5
+#define LQ_ROUND_SUPPLIED_FIXED 5
 
 typedef struct lq_mx_state {
   void* q_state;         /* device; see layouts above                                           */
@@ -89,7 +90,7 @@ typedef struct lq_rounding {
   uint64_t seed;         /* Philox key (low word k0, high word k1)                               */
   uint64_t step;         /* PHILOX_LAYERED: counter word; PHILOX_REF: unused (see rng_offset)    */
   uint64_t rng_offset;   /* PHILOX_REF: RNG_OFFSET = step * numel of the reference (:659, :716)  */
-  const uint32_t* words; /* SUPPLIED / SUPPLIED16: device, one word per value, [B,H,P,N] dense   */
+  const uint32_t* words; /* SUPPLIED / SUPPLIED_FIXED: device, one word per value, [B,H,P,N]   */
   const uint64_t* step_counter; /* optional device counter read when the kernel runs: its value is
                             added to `step`, and value * numel(state) to `rng_offset`, so that a
                             launch recorded once (CUDA graph) draws fresh numbers on every replay;
@@ -188,7 +189,9 @@ typedef struct lq_int4_decode_args {
 
 int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_stream);
 
-/* Bytes of zero-initialised scratch lq_int4_decode_attn needs for up to max_splits splits. */
+/* Bytes of zero-initialised scratch lq_int4_decode_attn needs for up to max_splits splits: a fixed
+ * 256 KiB of ticket counters (kept zero by the kernel) followed by the per-split partial results.
+ * A buffer may be reused for any problem it is large enough for.                               */
 size_t lq_int4_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                                       int32_t max_splits);
 /* The split count the library would pick for this problem on the current device (>= 1). */

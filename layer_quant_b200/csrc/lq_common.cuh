@@ -83,6 +83,39 @@ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint3
   return Philox4{c0, c1, c2, c3};
 }
 
+// Same generator with the ten round keys precomputed (k0 + r * 0x9E3779B9, k1 + r * 0xBB67AE85 at
+// rk[2r], rk[2r + 1]); when rk lives in kernel parameters the keys cost no instruction.
+struct PhiloxKeys {
+  uint32_t rk[20];
+};
+
+inline PhiloxKeys make_philox_keys(uint64_t seed) {
+  PhiloxKeys k;
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    k.rk[2 * r] = k0;
+    k.rk[2 * r + 1] = k1;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return k;
+}
+
+__device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const PhiloxKeys& keys) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t pb = static_cast<uint64_t>(0xCD9E8D57u) * c2;
+    const uint64_t pa = static_cast<uint64_t>(0xD2511F53u) * c0;
+    const uint32_t n0 = static_cast<uint32_t>(pb >> 32) ^ c1 ^ keys.rk[2 * r];
+    const uint32_t n2 = static_cast<uint32_t>(pa >> 32) ^ c3 ^ keys.rk[2 * r + 1];
+    c1 = static_cast<uint32_t>(pb);
+    c3 = static_cast<uint32_t>(pa);
+    c0 = n0;
+    c2 = n2;
+  }
+  return Philox4{c0, c1, c2, c3};
+}
+
 // Word -> uniform float in [0, 1) exactly as tl.rand does it: reinterpret as int32, fold the
 // negative half with x -> -x - 1, convert (round to nearest) and scale by fp32(4.6566127342e-10).
 __device__ __forceinline__ float word_to_uniform(uint32_t w) {

@@ -547,6 +547,13 @@ static int validate_cache(const lq_int4_cache& c, const char* who) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Workspace layout: a FIXED region of ticket counters first (one int32 per (batch, kv head), zero
+// between launches), then the per-split partial results.  The counter region does not move with
+// the problem size, so a buffer reused for a larger problem never finds stale partial results
+// where it expects zeroed tickets.
+constexpr size_t kMaxTickets = 65536;
+constexpr size_t kTicketBytes = kMaxTickets * sizeof(int32_t);
+
 static int pick_splits(int batch, int kv_heads, int ctx_len) {
   const int ntiles = std::max(1, (ctx_len + kTile - 1) / kTile);
   const int sms = sm_count();
@@ -635,10 +642,9 @@ LQ_EXPORT int lq_int4_kv_append(const lq_int4_cache* cache, const void* k, const
 LQ_EXPORT size_t lq_int4_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                                                  int32_t max_splits) {
   if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_splits <= 0) return 0;
-  const size_t counters = align_up(static_cast<size_t>(batch) * kv_heads * sizeof(int32_t), 256);
   const size_t ml = align_up(static_cast<size_t>(batch) * q_heads * max_splits * 2 * sizeof(float), 256);
   const size_t acc = static_cast<size_t>(batch) * q_heads * max_splits * head_dim * sizeof(float);
-  return counters + ml + acc;
+  return kTicketBytes + ml + acc;
 }
 
 LQ_EXPORT int32_t lq_int4_decode_auto_splits(int32_t batch, int32_t kv_heads, int32_t seq_len) {
@@ -692,7 +698,10 @@ LQ_EXPORT int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_st
                   a.workspace ? a.workspace_bytes : (size_t)0);
     LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(a.workspace) % 256 == 0, "lq_int4_decode_attn: workspace must be 256-byte aligned");
     uint8_t* w = static_cast<uint8_t*>(a.workspace);
-    const size_t counters = align_up(static_cast<size_t>(c.batch) * c.kv_heads * sizeof(int32_t), 256);
+    if (static_cast<size_t>(c.batch) * c.kv_heads > kMaxTickets)
+      return fail(LQ_ERR_UNSUPPORTED, "lq_int4_decode_attn: batch * kv_heads = %lld exceeds %zu with more than one split",
+                  (long long)c.batch * c.kv_heads, kMaxTickets);
+    const size_t counters = kTicketBytes;
     const size_t ml = align_up(static_cast<size_t>(c.batch) * a.q_heads * splits * 2 * sizeof(float), 256);
     p.counters = reinterpret_cast<int32_t*>(w);
     p.part_ml = reinterpret_cast<float*>(w + counters);

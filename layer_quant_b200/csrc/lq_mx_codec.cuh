@@ -4,6 +4,13 @@
 // quantiser (:559-568), with IEEE fp32 division and a correctly rounded log2 as the canonical
 // float semantics.  The exponent needs neither a division nor a logarithm here: it is a table
 // look-up on the exponent field of the block maximum plus one mantissa compare (lq_exp_table.h).
+//
+// Instruction budget.  On B200 the integer / logic / compare / min-max / byte-permute pipe issues
+// at half the rate of the FMA pipe, and at HBM speed an MX8 value may cost about 6 such
+// instructions and 12 issue slots in total.  The code below therefore keeps work on the FMA pipe
+// wherever the result is bit-identical: scale selection, micro-exponent bits and int -> byte
+// conversion are done with exact float arithmetic and magic constants instead of selects, shifts
+// and conversions; bytes are gathered with one byte-permute per value.
 #pragma once
 
 #include "lq_common.cuh"
@@ -32,26 +39,48 @@ __device__ __forceinline__ float mx_decode_scale(uint32_t e, uint32_t micro) {
 
 // Rounding context of one 16-value block.
 struct MxRoundCtx {
-  uint32_t k0, k1;      // Philox key
-  uint64_t counter;     // PHILOX_REF: counter of value 0 of the block; PHILOX_LAYERED: index of its first 8-group
-  uint32_t wrap32;      // PHILOX_REF: counters are taken modulo 2^32 with a zero high word
-  uint32_t step, layer; // PHILOX_LAYERED
-  const uint32_t* words; // SUPPLIED*: 16 words of this block
+  uint64_t counter;      // PHILOX_REF: counter of value 0 of the block; PHILOX_LAYERED: index of the block
+  uint32_t wrap32;       // PHILOX_REF: counters are taken modulo 2^32 with a zero high word
+  uint32_t step, layer;  // PHILOX_LAYERED
+  const uint32_t* words; // SUPPLIED / SUPPLIED_FIXED: 16 words of this block
 };
 
+// 1.0f if a > b else 0.0f, as one FSET.
+__device__ __forceinline__ float set_gt(float a, float b) {
+  float r;
+  asm("set.gt.f32.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+// Byte 1 of four words -> one word (byte k from word k): three byte-permutes.
+__device__ __forceinline__ uint32_t gather_byte1(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  const uint32_t ab = __byte_perm(a, b, 0x0051);  // [a.1, b.1, a.0, a.0]
+  const uint32_t cd = __byte_perm(c, d, 0x0051);
+  return __byte_perm(ab, cd, 0x5410);             // [ab.0, ab.1, cd.0, cd.1]
+}
+
+constexpr float kByteMagic = 49152.0f;  // 1.5 * 2^15: ulp 2^-8, mantissa bits 8..15 = integer part mod 256
+
 // Encodes h[0..15].  codes[w] holds values 4w..4w+3 as int8 lanes; micro_bits bit i = pair i.
+//
+// Two rounding rules:
+//  * reference rule (HALF_UP, HALF_EVEN, PHILOX_REF, SUPPLIED): a = min(|h| / scale, M), level from
+//    floor(a + .5) / rint(a) / floor(a) + (u < a - floor(a)), sign restored afterwards -- the
+//    reference's expressions, evaluated with the same fp32 operations;
+//  * fixed-point rule (PHILOX_LAYERED, SUPPLIED_FIXED): t = fl32(h / scale + 49152 + r8 / 256) in one
+//    FMA, q = floor(t) - 49152, i.e. stochastic rounding with an 8-bit uniform draw r8; q (two's
+//    complement) is byte 1 of t's bit pattern.  No clamp is needed: |h| / scale never exceeds
+//    M + 2^-9 (the few-ulp overshoot of the rounded log2 is orders of magnitude smaller).
 template <int BITS, int MODE>
 __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsigned int* __restrict__ cut_table,
-                                                const MxRoundCtx& ctx, uint32_t (&codes)[4], uint32_t& exp_byte,
-                                                uint32_t& micro_bits) {
+                                                const MxRoundCtx& ctx, const PhiloxKeys& keys, uint32_t (&codes)[4],
+                                                uint32_t& exp_byte, uint32_t& micro_bits) {
   constexpr float M = MxFormat<BITS>::kMax;
-  float pair_amax[8];
-  float amax = 0.0f;
+  constexpr bool kFixed = (MODE == LQ_ROUND_PHILOX_LAYERED || MODE == LQ_ROUND_SUPPLIED_FIXED);
+  float pa[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    pair_amax[j] = fmaxf(fabsf(h[2 * j]), fabsf(h[2 * j + 1]));
-    amax = fmaxf(amax, pair_amax[j]);
-  }
+  for (int j = 0; j < 8; ++j) pa[j] = fmaxf(fabsf(h[2 * j]), fabsf(h[2 * j + 1]));
+  const float amax = fmaxf(fmaxf(fmaxf(pa[0], pa[1]), fmaxf(pa[2], pa[3])), fmaxf(fmaxf(pa[4], pa[5]), fmaxf(pa[6], pa[7])));
   // biased = clamp(ceil(log2(max(amax / 2M, 1e-30))) + 127, 1, 254): always in [28, 252]
   const uint32_t abits = __float_as_uint(amax);
   const uint32_t field = abits >> 23;
@@ -59,88 +88,96 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
   biased = biased < 28 ? 28 : biased;
   exp_byte = static_cast<uint32_t>(biased);
   // amax == 0 makes the reference use base 1.0; every mantissa is 0 with either base.
-  const float base = __uint_as_float(static_cast<uint32_t>(biased) << 23);
-  const float thresh = M * base;  // exact
-  const float inv0 = __uint_as_float(static_cast<uint32_t>(254 - biased) << 23);  // 1 / base
-  const float inv1 = __uint_as_float(static_cast<uint32_t>(253 - biased) << 23);  // 1 / (2 base)
+  const float thresh = M * __uint_as_float(static_cast<uint32_t>(biased) << 23);       // M * base, exact
+  const float inv0 = __uint_as_float(static_cast<uint32_t>(254 - biased) << 23);        // 1 / base
+  const float neg_half_inv0 = -0.5f * inv0;
 
-  uint32_t supplied[16];
-  if (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED16) {
+  uint32_t rnd[16];  // SUPPLIED*: one word per value
+  if (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED_FIXED) {
     const uint4* w4 = reinterpret_cast<const uint4*>(ctx.words);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 v = __ldg(w4 + i);
-      supplied[4 * i] = v.x; supplied[4 * i + 1] = v.y; supplied[4 * i + 2] = v.z; supplied[4 * i + 3] = v.w;
+      rnd[4 * i] = v.x; rnd[4 * i + 1] = v.y; rnd[4 * i + 2] = v.z; rnd[4 * i + 3] = v.w;
     }
   }
-  uint32_t r16[16];
+  uint32_t pw[4] = {0u, 0u, 0u, 0u};  // PHILOX_LAYERED: 16 random bytes, value i = byte i & 3 of word i >> 2
   if (MODE == LQ_ROUND_PHILOX_LAYERED) {
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      const uint64_t idx = ctx.counter + g;
-      const Philox4 r = philox4x32_10(static_cast<uint32_t>(idx), static_cast<uint32_t>(idx >> 32), ctx.step, ctx.layer,
-                                      ctx.k0, ctx.k1);
-      const uint32_t w[4] = {r.w0, r.w1, r.w2, r.w3};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        r16[8 * g + 2 * j] = w[j] & 0xFFFFu;
-        r16[8 * g + 2 * j + 1] = w[j] >> 16;
-      }
-    }
+    const Philox4 r = philox4x32_10(static_cast<uint32_t>(ctx.counter), static_cast<uint32_t>(ctx.counter >> 32), ctx.step,
+                                    ctx.layer, keys);
+    pw[0] = r.w0; pw[1] = r.w1; pw[2] = r.w2; pw[3] = r.w3;
   }
 
-  micro_bits = 0;
-  codes[0] = codes[1] = codes[2] = codes[3] = 0;
+  float macc = 0.0f;  // sum of 2^j over pairs with the micro-exponent set (exact)
+  uint32_t tb[16];    // bit patterns whose byte 1 is the code
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const bool mic = pair_amax[i >> 1] > thresh;
-    if ((i & 1) == 0) micro_bits |= (mic ? 1u : 0u) << (i >> 1);
-    const float inv = mic ? inv1 : inv0;
-    int q;
-    if (MODE == LQ_ROUND_PHILOX_LAYERED || MODE == LQ_ROUND_SUPPLIED16) {
-      // 16.16 fixed point of v/scale + 64 sits in the mantissa of a float in [128, 256)
-      float t = fmaf(h[i], inv, 192.0f);
-      t = fminf(fmaxf(t, 192.0f - M), 192.0f + M);
-      const uint32_t r = (MODE == LQ_ROUND_SUPPLIED16) ? (supplied[i] & 0xFFFFu) : r16[i];
-      q = static_cast<int>(((__float_as_uint(t) + r) >> 16) & 0xFFu) - 64;
-    } else {
-      const float a = fminf(fabsf(h[i]) * inv, M);
-      float lvl;
-      if (MODE == LQ_ROUND_HALF_UP) {
-        lvl = floorf(a + 0.5f);
-      } else if (MODE == LQ_ROUND_HALF_EVEN) {
-        lvl = rintf(a);
+  for (int j = 0; j < 8; ++j) {
+    const float micf = set_gt(pa[j], thresh);
+    const float inv = fmaf(micf, neg_half_inv0, inv0);  // 1 / (base * 2^micro), exact
+    macc = fmaf(micf, static_cast<float>(1 << j), macc);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = 2 * j + k;
+      float t;
+      if (kFixed) {
+        const uint32_t c = (MODE == LQ_ROUND_SUPPLIED_FIXED) ? (0x47400000u | (rnd[i] & 0xFFu))
+                                                             : __byte_perm(pw[i >> 2], 0x47400000u, 0x7650 + (i & 3));
+        t = fmaf(h[i], inv, __uint_as_float(c));
       } else {
-        uint32_t w;
-        if (MODE == LQ_ROUND_SUPPLIED) {
-          w = supplied[i];
-        } else {  // the reference's stream: one Philox block per value, word 0
-          const uint64_t c = ctx.counter + i;
-          w = philox4x32_10(static_cast<uint32_t>(c), ctx.wrap32 ? 0u : static_cast<uint32_t>(c >> 32), 0u, 0u, ctx.k0,
-                            ctx.k1).w0;
+        const float a = fminf(fabsf(h[i]) * inv, M);
+        float lvl;
+        if (MODE == LQ_ROUND_HALF_UP) {
+          lvl = floorf(a + 0.5f);
+        } else if (MODE == LQ_ROUND_HALF_EVEN) {
+          lvl = rintf(a);
+        } else {
+          uint32_t w;
+          if (MODE == LQ_ROUND_SUPPLIED) {
+            w = rnd[i];
+          } else {  // the reference's stream: one Philox block per value, word 0
+            const uint64_t c = ctx.counter + i;
+            w = philox4x32_10(static_cast<uint32_t>(c), ctx.wrap32 ? 0u : static_cast<uint32_t>(c >> 32), 0u, 0u, keys).w0;
+          }
+          const float fl = floorf(a);
+          lvl = fl + set_gt(a - fl, word_to_uniform(w));  // (u < a - fl) ? 1 : 0
         }
-        const float fl = floorf(a);
-        lvl = fl + ((word_to_uniform(w) < a - fl) ? 1.0f : 0.0f);
+        lvl = fminf(lvl, M);
+        t = copysignf(lvl, h[i]) + kByteMagic;  // exact; byte 1 = two's complement of the signed level
       }
-      lvl = fminf(lvl, M);
-      q = static_cast<int>(lvl);
-      q = h[i] < 0.0f ? -q : q;
+      tb[i] = __float_as_uint(t);
     }
-    codes[i >> 2] |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * (i & 3));
   }
+#pragma unroll
+  for (int w = 0; w < 4; ++w) codes[w] = gather_byte1(tb[4 * w], tb[4 * w + 1], tb[4 * w + 2], tb[4 * w + 3]);
+  micro_bits = __float_as_uint(macc + 8388608.0f) & 0xFFu;
 }
 
-// int8 lanes of `codes` times `scale` (per pair) -> fp32, using the 2^23 magic-number conversion.
+// int8 lanes of `codes` times 2^(e - 127 + micro of the pair) -> fp32 (reference :132).
+// Fast path (stored exponent in [1, 229], everything the codec itself writes is in [28, 252] and
+// states of realistic magnitude stay far below 229): byte -> float by one byte-permute into the
+// mantissa of 2^15 (value 32768 + 128 + q), then ONE exact FMA per value: (32896 + q) * s - 32896 * s.
+// The per-pair scale is built on the FMA pipe from the micro bit: bits(s) = e << 23 + micro << 23.
 __device__ __forceinline__ void mx_decode_block(const uint32_t (&codes)[4], uint32_t e, uint32_t micro_bits, float (&h)[16]) {
-  const float s0 = mx_decode_scale(e, 0), s1 = mx_decode_scale(e, 1);
+  if (e >= 1u && e <= 229u) {
+    const uint32_t ebits = e << 23;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const uint32_t biased = codes[w] ^ 0x80808080u;  // q + 128 as unsigned bytes
+    for (int j = 0; j < 8; ++j) {
+      const float s = __uint_as_float((micro_bits & (1u << j)) * (1u << (23 - j)) + ebits);
+      const float cs = -32896.0f * s;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int i = 4 * w + k;
-      const float f = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650 + k)) - 8388736.0f;  // exact q
-      h[i] = f * (((micro_bits >> (i >> 1)) & 1u) ? s1 : s0);
+      for (int k = 0; k < 2; ++k) {
+        const int i = 2 * j + k;
+        const uint32_t biased = codes[i >> 2] ^ 0x80808080u;  // q + 128 as unsigned bytes
+        const float f = __uint_as_float(__byte_perm(biased, 0x47000000u, 0x7604 | ((i & 3) << 4)));  // 32768 + 128 + q
+        h[i] = fmaf(f, s, cs);
+      }
+    }
+  } else {  // exponents no quantiser emits: plain, overflow-safe form
+    const float s0 = mx_decode_scale(e, 0), s1 = mx_decode_scale(e, 1);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int q = static_cast<int>(static_cast<int8_t>((codes[i >> 2] >> (8 * (i & 3))) & 0xFFu));
+      h[i] = static_cast<float>(q) * (((micro_bits >> (i >> 1)) & 1u) ? s1 : s0);
     }
   }
 }
@@ -151,14 +188,15 @@ __device__ __forceinline__ void mx4_nibbles_to_bytes(uint32_t lo, uint32_t hi, u
   const uint32_t src[2] = {lo, hi};
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t x = (src[s] >> (16 * half)) & 0xFFFFu;  // 4 nibbles
-      // spread nibble k to byte k, then sign-extend each byte from bit 3
-      uint32_t b = (x & 0xFu) | ((x & 0xF0u) << 4) | ((x & 0xF00u) << 8) | ((x & 0xF000u) << 12);
-      b |= ((b & 0x08080808u) * 0x1Eu) & 0xF0F0F0F0u;
-      codes[2 * s + half] = b;
-    }
+    // even values sit in the low nibbles of the 4 bytes, odd values in the high nibbles
+    const uint32_t ev = src[s] & 0x0F0F0F0Fu, od = (src[s] >> 4) & 0x0F0F0F0Fu;
+    // interleave: result word 0 = values 0..3 = [ev.0, od.0, ev.1, od.1], word 1 = [ev.2, od.2, ev.3, od.3]
+    uint32_t w0 = __byte_perm(ev, od, 0x5140), w1 = __byte_perm(ev, od, 0x7362);
+    // sign-extend each byte from bit 3
+    w0 |= (w0 & 0x08080808u) * 0x1Eu;
+    w1 |= (w1 & 0x08080808u) * 0x1Eu;
+    codes[2 * s] = w0;
+    codes[2 * s + 1] = w1;
   }
 }
 
@@ -166,14 +204,10 @@ __device__ __forceinline__ void mx4_bytes_to_nibbles(const uint32_t (&codes)[4],
   uint32_t out[2];
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
-    uint32_t acc = 0;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t b = codes[2 * s + half] & 0x0F0F0F0Fu;
-      const uint32_t x = (b & 0xFu) | ((b >> 4) & 0xF0u) | ((b >> 8) & 0xF00u) | ((b >> 12) & 0xF000u);
-      acc |= x << (16 * half);
-    }
-    out[s] = acc;
+    const uint32_t w0 = codes[2 * s] & 0x0F0F0F0Fu, w1 = codes[2 * s + 1] & 0x0F0F0F0Fu;
+    const uint32_t ev = __byte_perm(w0, w1, 0x6420);  // values 0, 2, 4, 6
+    const uint32_t od = __byte_perm(w0, w1, 0x7531);  // values 1, 3, 5, 7
+    out[s] = ev | (od << 4);
   }
   lo = out[0];
   hi = out[1];

@@ -31,6 +31,46 @@ struct MxBlockIO {
   static constexpr bool kNibbles = (BITS == 4 && LAYOUT == LQ_MX_LAYOUT_PACKED);
   static constexpr int kQBytes = kNibbles ? 8 : 16;
 
+  static constexpr int kMicroBytes = (LAYOUT == LQ_MX_LAYOUT_PACKED) ? 1 : 8;
+
+  // One block through plain pointers (dense states: the caller does the address arithmetic once).
+  __device__ __forceinline__ static MxRaw load_ptr(const uint8_t* q, const uint8_t* e, const uint8_t* m) {
+    MxRaw r;
+    if (kNibbles) {
+      const uint2 v = *reinterpret_cast<const uint2*>(q);
+      r.q = make_uint4(v.x, v.y, 0u, 0u);
+    } else {
+      r.q = *reinterpret_cast<const uint4*>(q);
+    }
+    r.e = *e;
+    if (LAYOUT == LQ_MX_LAYOUT_PACKED) {
+      r.mic = *m;
+    } else {
+      const uint2 mm = *reinterpret_cast<const uint2*>(m);
+      r.mic = (((mm.x & 0x01010101u) * 0x10204080u) >> 28) | ((((mm.y & 0x01010101u) * 0x10204080u) >> 28) << 4);
+    }
+    return r;
+  }
+
+  __device__ __forceinline__ static void store_ptr(uint8_t* q, uint8_t* e, uint8_t* m, const uint32_t (&codes)[4], uint32_t ev,
+                                                   uint32_t mic) {
+    if (kNibbles) {
+      uint32_t lo, hi;
+      mx4_bytes_to_nibbles(codes, lo, hi);
+      *reinterpret_cast<uint2*>(q) = make_uint2(lo, hi);
+    } else {
+      *reinterpret_cast<uint4*>(q) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    }
+    *e = static_cast<uint8_t>(ev);
+    if (LAYOUT == LQ_MX_LAYOUT_PACKED) {
+      *m = static_cast<uint8_t>(mic);
+    } else {
+      const uint32_t lo = ((mic & 0xFu) * 0x00204081u) & 0x01010101u;
+      const uint32_t hi = (((mic >> 4) & 0xFu) * 0x00204081u) & 0x01010101u;
+      *reinterpret_cast<uint2*>(m) = make_uint2(lo, hi);
+    }
+  }
+
   __device__ __forceinline__ static MxRaw load(const lq_mx_state& s, int64_t qrow, int64_t erow, int64_t mrow, int blk) {
     MxRaw r;
     const uint8_t* q = static_cast<const uint8_t*>(s.q_state) + qrow + blk * kQBytes;
@@ -79,19 +119,34 @@ struct MxBlockIO {
   }
 };
 
-// `numel` = values in the whole state: the reference advances its Philox offset by it every step.
-template <int MODE>
-__device__ __forceinline__ MxRoundCtx make_round_ctx(const lq_rounding& r, uint64_t lin, uint64_t numel) {
-  MxRoundCtx c;
-  c.k0 = static_cast<uint32_t>(r.seed);
-  c.k1 = static_cast<uint32_t>(r.seed >> 32);
+// Rounding state that is the same for every block a thread handles.  `numel` = values in the whole
+// state: the reference advances its Philox offset by it every step.
+struct MxRoundBase {
+  uint32_t wrap32, step, layer;
+  uint64_t offset;
+  const uint32_t* words;
+};
+
+__device__ __forceinline__ MxRoundBase make_round_base(const lq_rounding& r, uint64_t numel) {
+  MxRoundBase b;
   const uint64_t extra = r.step_counter ? __ldg(reinterpret_cast<const unsigned long long*>(r.step_counter)) : 0ull;
-  const uint64_t rng_offset = r.rng_offset + extra * numel;
-  c.wrap32 = rng_offset < (1ull << 32) ? 1u : 0u;
-  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 3) : (rng_offset + lin);
-  c.step = static_cast<uint32_t>(r.step + extra);
-  c.layer = r.layer;
-  c.words = (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED16) ? r.words + lin : nullptr;
+  b.offset = r.rng_offset + extra * numel;
+  b.wrap32 = b.offset < (1ull << 32) ? 1u : 0u;
+  b.step = static_cast<uint32_t>(r.step + extra);
+  b.layer = r.layer;
+  b.words = r.words;
+  return b;
+}
+
+// Context of the block whose first value has linear index `lin` (a multiple of 16).
+template <int MODE>
+__device__ __forceinline__ MxRoundCtx round_ctx_at(const MxRoundBase& b, uint64_t lin) {
+  MxRoundCtx c;
+  c.wrap32 = b.wrap32;
+  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 4) : (b.offset + lin);
+  c.step = b.step;
+  c.layer = b.layer;
+  c.words = (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED_FIXED) ? b.words + lin : nullptr;
   return c;
 }
 
@@ -100,17 +155,53 @@ struct MxUpdateDerived {
   int32_t lpr_log2;    // lanes per row = 1 << lpr_log2 >= nblk
   int32_t dt_uniform;  // dt and dt_bias do not depend on the row (dim) index
   int32_t a_scalar;    // A depends on the head only
+  int32_t heads_per_cta;  // consecutive heads of one B/C group handled by one CTA
+  PhiloxKeys keys;        // round keys of rounding.seed
 };
 
 __device__ __forceinline__ float softplus_ref(float x) { return x <= 20.0f ? logf(1.0f + expf(x)) : x; }
 
+// 16 consecutive B or C values of (batch b, group grp) starting at column n0, as floats.  Contiguous
+// 16-bit operands take two 128-bit loads; anything else goes value by value.
+__device__ __forceinline__ void load_bc16(const void* base, const int64_t (&st)[3], int dtype, int b, int grp, int n0, float (&v)[16]) {
+  const int64_t off = b * st[0] + grp * st[1] + n0 * st[2];
+  if (dtype != LQ_F32 && st[2] == 1 && ((reinterpret_cast<uintptr_t>(base) + 2 * off) & 15) == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + off);
+    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (dtype == LQ_BF16) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = load_as_float(base, off + i * st[2], dtype);
+  }
+}
+
+// One CTA = `hpc` consecutive heads of one (batch, B/C group): B and C are fetched once and stay in
+// registers for hpc * dim rows.  gridDim.x = batch * (heads / hpc).
 template <int BITS, int LAYOUT, int MODE>
-__global__ void __launch_bounds__(kUpdateThreads) mx_state_update_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
+__global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
   using IO = MxBlockIO<BITS, LAYOUT>;
+  extern __shared__ float smem_xy[];  // x of the CTA's rows, <h', C> of the rows, per-head dt and exp(A dt)
   const lq_mx_state& s = a.state;
   const int H = s.heads, P = s.dim, N = s.dstate;
-  const int b = blockIdx.x / H;
-  const int h = blockIdx.x - b * H;
+  const int hpc = d.heads_per_cta;
+  float* sx = smem_xy;
+  float* sy = sx + hpc * P;
+  float* sdt = sy + hpc * P;
+  float* sdA = sdt + hpc;
+  const int chunks = H / hpc;
+  const int b = blockIdx.x / chunks;
+  const int h0 = (blockIdx.x - b * chunks) * hpc;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int blk = lane & ((1 << d.lpr_log2) - 1);
   const int rsub = lane >> d.lpr_log2;
@@ -118,77 +209,208 @@ __global__ void __launch_bounds__(kUpdateThreads) mx_state_update_kernel(const l
   const int rows_per_pass = rows_per_warp * (kUpdateThreads / 32);
   const bool blk_ok = blk < d.nblk;
   const int n0 = blk * 16;
-  const int grp = h / (H / a.ngroups);
+  const int grp = h0 / (H / a.ngroups);  // the same for every head of the CTA
   const unsigned int* cut = mx_exp_cut_table<BITS>();
 
-  // B and C of this head's group, this lane's 16 columns
-  float Bv[16], Cv[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    Bv[i] = blk_ok ? load_as_float(a.B, b * a.B_stride[0] + grp * a.B_stride[1] + (n0 + i) * a.B_stride[2], a.B_dtype) : 0.0f;
-    Cv[i] = blk_ok ? load_as_float(a.C, b * a.C_stride[0] + grp * a.C_stride[1] + (n0 + i) * a.C_stride[2], a.C_dtype) : 0.0f;
-  }
-
-  auto row_dt = [&](int p) {
+  auto row_dt = [&](int h, int p) {
     float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1] + p * a.dt_stride[2], a.dt_dtype);
     if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0] + p * a.dt_bias_stride[1], a.dt_bias_dtype);
     if (a.dt_softplus) dt = softplus_ref(dt);
     return dt;
   };
-  float dt_h = 0.0f, dA_h = 0.0f;
-  if (d.dt_uniform) {
-    dt_h = row_dt(0);
-    if (d.a_scalar) dA_h = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt_h);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) Bv[i] *= dt_h;  // (B * dt), then * x per row: the reference's order
+  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
+    const int hh = i / P, p = i - hh * P;
+    sx[i] = load_as_float(a.x, b * a.x_stride[0] + (h0 + hh) * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
+  }
+  if (d.dt_uniform && threadIdx.x < hpc) {
+    const float dt = row_dt(h0 + threadIdx.x, 0);
+    sdt[threadIdx.x] = dt;
+    sdA[threadIdx.x] = d.a_scalar ? expf(load_as_float(a.A, (h0 + threadIdx.x) * a.A_stride[0], a.A_dtype) * dt) : 0.0f;
   }
 
-  const int64_t qbase = b * s.q_stride[0] + h * s.q_stride[1];
-  const int64_t ebase = b * s.exp_stride[0] + h * s.exp_stride[1];
-  const int64_t mbase = b * s.micro_stride[0] + h * s.micro_stride[1];
-
-  int p0 = warp * rows_per_warp;
-  MxRaw cur = {make_uint4(0, 0, 0, 0), 127u, 0u};
-  if (blk_ok && p0 + rsub < P)
-    cur = IO::load(s, qbase + (p0 + rsub) * s.q_stride[2], ebase + (p0 + rsub) * s.exp_stride[2],
-                   mbase + (p0 + rsub) * s.micro_stride[2], blk);
+  // B and C of the group, this lane's 16 columns
+  float Bv[16], Cv[16];
+  if (blk_ok) {
+    load_bc16(a.B, a.B_stride, a.B_dtype, b, grp, n0, Bv);
+    load_bc16(a.C, a.C_stride, a.C_dtype, b, grp, n0, Cv);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) Bv[i] = Cv[i] = 0.0f;
+  }
+  const bool hoisted = d.dt_uniform && d.a_scalar;
+  const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * N);
+  __syncthreads();
 
 #pragma unroll 1
-  for (; p0 < P; p0 += rows_per_pass) {
-    const int p = p0 + rsub;
-    const bool active = blk_ok && p < P;
-    // issue the next row's loads before working on this one
-    const int pn = p + rows_per_pass;
-    MxRaw nxt = {make_uint4(0, 0, 0, 0), 127u, 0u};
-    if (blk_ok && pn < P)
-      nxt = IO::load(s, qbase + pn * s.q_stride[2], ebase + pn * s.exp_stride[2], mbase + pn * s.micro_stride[2], blk);
+  for (int hh = 0; hh < hpc; ++hh) {
+    const int h = h0 + hh;
+    const float dt_h = d.dt_uniform ? sdt[hh] : 0.0f;
+    const float dA_h = sdA[hh];
+    const uint64_t lin_head = (static_cast<uint64_t>(b) * H + h) * P * static_cast<uint64_t>(N) + n0;
+    const int64_t qbase = b * s.q_stride[0] + h * s.q_stride[1];
+    const int64_t ebase = b * s.exp_stride[0] + h * s.exp_stride[1];
+    const int64_t mbase = b * s.micro_stride[0] + h * s.micro_stride[1];
+    const float* sxh = sx + hh * P;
+    float* syh = sy + hh * P;
 
-    float y = 0.0f;
-    float xv = 0.0f;
-    if (active) {
+    int p0 = warp * rows_per_warp;
+    MxRaw cur = {make_uint4(0, 0, 0, 0), 127u, 0u};
+    if (blk_ok && p0 + rsub < P)
+      cur = IO::load(s, qbase + (p0 + rsub) * s.q_stride[2], ebase + (p0 + rsub) * s.exp_stride[2],
+                     mbase + (p0 + rsub) * s.micro_stride[2], blk);
+#pragma unroll 1
+    for (; p0 < P; p0 += rows_per_pass) {
+      const int p = p0 + rsub;
+      const bool active = blk_ok && p < P;
+      // issue the next row's loads before working on this one
+      const int pn = p + rows_per_pass;
+      MxRaw nxt = {make_uint4(0, 0, 0, 0), 127u, 0u};
+      if (blk_ok && pn < P)
+        nxt = IO::load(s, qbase + pn * s.q_stride[2], ebase + pn * s.exp_stride[2], mbase + pn * s.micro_stride[2], blk);
+
+      float y = 0.0f;
+      if (active) {
+        uint32_t codes[4];
+        IO::codes_of(cur, codes);
+        float hv[16];
+        mx_decode_block(codes, cur.e, cur.mic, hv);
+        const float xv = sxh[p];
+        if (hoisted) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + (Bv[i] * dt_h) * xv;  // (B dt) x: the reference's order
+        } else {
+          const float dt = d.dt_uniform ? dt_h : row_dt(h, p);
+          if (d.a_scalar) {
+            const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + (Bv[i] * dt) * xv;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
+              hv[i] = hv[i] * expf(Ai * dt) + (Bv[i] * dt) * xv;
+            }
+          }
+        }
+        float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          y0 = fmaf(hv[i], Cv[i], y0);
+          y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
+          y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
+          y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
+        }
+        y = (y0 + y1) + (y2 + y3);
+
+        const uint64_t lin = lin_head + static_cast<uint64_t>(static_cast<uint32_t>(p) * static_cast<uint32_t>(N));
+        if (a.h_out) {
+          float4* dst = reinterpret_cast<float4*>(a.h_out + lin);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_float4(hv[4 * i], hv[4 * i + 1], hv[4 * i + 2], hv[4 * i + 3]);
+        }
+        const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
+        uint32_t e_new, mic_new;
+        mx_encode_block<BITS, MODE>(hv, cut, ctx, d.keys, codes, e_new, mic_new);
+        IO::store(s, qbase + p * s.q_stride[2], ebase + p * s.exp_stride[2], mbase + p * s.micro_stride[2], blk, codes, e_new,
+                  mic_new);
+      }
+      // y = <h', C> over the row: reduce across the lanes that share it
+      for (int o = (1 << d.lpr_log2) >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+      if (active && blk == 0) syh[p] = y;
+      cur = nxt;
+    }
+  }
+  __syncthreads();
+  // y = <h', C> + D x (* z), stored for all the CTA's rows at once
+  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
+    const int hh = i / P, p = i - hh * P, h = h0 + hh;
+    float y = sy[i];
+    if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
+    if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
+    store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
+  }
+}
+
+// Fast path of the fused update: the shape every Mamba2 decode step has.  Requirements (checked
+// on the host): dense state tensors, dt / dt_bias / A per head only, dstate / 16 a power of two,
+// dim a multiple of the rows one CTA pass covers, no h_out.  Every lane is then always active, all
+// addresses are one per-CTA 64-bit base plus 32-bit offsets bumped by a constant, and the loop body
+// has no divergent branch.
+template <int BITS, int LAYOUT, int MODE>
+__global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
+  using IO = MxBlockIO<BITS, LAYOUT>;
+  extern __shared__ float smem_xy[];
+  const lq_mx_state& s = a.state;
+  const int H = s.heads, P = s.dim;
+  const int hpc = d.heads_per_cta;
+  float* sx = smem_xy;
+  float* sy = sx + hpc * P;
+  float* sdt = sy + hpc * P;
+  float* sdA = sdt + hpc;
+  const int chunks = H / hpc;
+  const int b = blockIdx.x / chunks;
+  const int h0 = (blockIdx.x - b * chunks) * hpc;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blk = lane & (d.nblk - 1);
+  const int rsub = lane >> d.lpr_log2;
+  const int rows_per_warp = 32 >> d.lpr_log2;
+  const int rows_per_pass = rows_per_warp * (kUpdateThreads / 32);
+  const int n0 = blk * 16;
+  const int grp = h0 / (H / a.ngroups);
+  const unsigned int* cut = mx_exp_cut_table<BITS>();
+
+  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
+    const int hh = i / P, p = i - hh * P;
+    sx[i] = load_as_float(a.x, b * a.x_stride[0] + (h0 + hh) * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
+  }
+  if (threadIdx.x < hpc) {
+    const int h = h0 + threadIdx.x;
+    float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1], a.dt_dtype);
+    if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0], a.dt_bias_dtype);
+    if (a.dt_softplus) dt = softplus_ref(dt);
+    sdt[threadIdx.x] = dt;
+    sdA[threadIdx.x] = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
+  }
+  float Bv[16], Cv[16];
+  load_bc16(a.B, a.B_stride, a.B_dtype, b, grp, n0, Bv);
+  load_bc16(a.C, a.C_stride, a.C_dtype, b, grp, n0, Cv);
+  const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * s.dstate);
+
+  // dense addressing: row r of the CTA (r in [0, hpc * P)), block blk
+  const uint32_t q_row = d.nblk * IO::kQBytes, m_row = d.nblk * IO::kMicroBytes, e_row = d.nblk;
+  const uint64_t row0 = (static_cast<uint64_t>(b) * H + h0) * P;
+  uint8_t* const qp = static_cast<uint8_t*>(s.q_state) + row0 * q_row;
+  uint8_t* const ep = s.shared_exp + row0 * e_row;
+  uint8_t* const mp = s.micro_exp + row0 * m_row;
+  const uint64_t lin0 = row0 * s.dstate;  // linear index of the CTA's first value
+  const uint32_t r_first = warp * rows_per_warp + rsub;
+  uint32_t qoff = r_first * q_row + blk * IO::kQBytes;
+  uint32_t eoff = r_first * e_row + blk;
+  uint32_t moff = r_first * m_row + blk * IO::kMicroBytes;
+  uint32_t loff = r_first * s.dstate + n0;  // value offset inside the CTA's rows (< 2^32: hpc * P * dstate)
+  uint32_t row = r_first;
+  const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
+                 dl = rows_per_pass * s.dstate;
+  const int iters_per_head = P / rows_per_pass;
+  __syncthreads();
+
+  MxRaw cur = IO::load_ptr(qp + qoff, ep + eoff, mp + moff);
+#pragma unroll 1
+  for (int hh = 0; hh < hpc; ++hh) {
+    const float dt_h = sdt[hh], dA_h = sdA[hh];
+    const bool last_head = hh + 1 == hpc;
+#pragma unroll 1
+    for (int it = 0; it < iters_per_head; ++it) {
+      MxRaw nxt = cur;
+      if (!(last_head && it + 1 == iters_per_head)) nxt = IO::load_ptr(qp + qoff + dq, ep + eoff + de, mp + moff + dm);
+
       uint32_t codes[4];
       IO::codes_of(cur, codes);
       float hv[16];
       mx_decode_block(codes, cur.e, cur.mic, hv);
-      xv = load_as_float(a.x, b * a.x_stride[0] + h * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
-      if (d.dt_uniform && d.a_scalar) {
+      const float xv = sx[row];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * xv;
-      } else {
-        const float dt = d.dt_uniform ? dt_h : row_dt(p);
-        const float bscale = d.dt_uniform ? 1.0f : dt;  // Bv already holds B * dt when dt is uniform
-        if (d.a_scalar) {
-          const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + (Bv[i] * bscale) * xv;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
-            hv[i] = hv[i] * expf(Ai * dt) + (Bv[i] * bscale) * xv;
-          }
-        }
-      }
+      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + (Bv[i] * dt_h) * xv;  // (B dt) x: the reference's order
       float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
@@ -197,38 +419,37 @@ __global__ void __launch_bounds__(kUpdateThreads) mx_state_update_kernel(const l
         y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
         y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
       }
-      y = (y0 + y1) + (y2 + y3);
+      float y = (y0 + y1) + (y2 + y3);
 
-      const uint64_t lin = ((static_cast<uint64_t>(b) * H + h) * P + p) * static_cast<uint64_t>(N) + n0;
-      if (a.h_out) {
-        float4* dst = reinterpret_cast<float4*>(a.h_out + lin);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_float4(hv[4 * i], hv[4 * i + 1], hv[4 * i + 2], hv[4 * i + 3]);
-      }
-      const MxRoundCtx ctx = make_round_ctx<MODE>(a.rounding, lin, static_cast<uint64_t>(s.batch) * H * P * N);
+      const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin0 + loff);
       uint32_t e_new, mic_new;
-      mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e_new, mic_new);
-      IO::store(s, qbase + p * s.q_stride[2], ebase + p * s.exp_stride[2], mbase + p * s.micro_stride[2], blk, codes, e_new,
-                mic_new);
+      mx_encode_block<BITS, MODE>(hv, cut, ctx, d.keys, codes, e_new, mic_new);
+      IO::store_ptr(qp + qoff, ep + eoff, mp + moff, codes, e_new, mic_new);
+
+      for (int o = d.nblk >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+      if (blk == 0) sy[row] = y;
+      cur = nxt;
+      qoff += dq; eoff += de; moff += dm; loff += dl; row += rows_per_pass;
     }
-    // y = <h', C> over the row: reduce across the lanes that share it
-    for (int o = (1 << d.lpr_log2) >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
-    if (active && blk == 0) {
-      if (a.D) y += xv * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
-      if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
-      store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
-    }
-    cur = nxt;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
+    const int hh = i / P, p = i - hh * P, h = h0 + hh;
+    float y = sy[i];
+    if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
+    if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
+    store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
   }
 }
 
 // ---- stand-alone codec kernels: one thread per 16-value block ----------------------------------
 template <int BITS, int LAYOUT, int MODE>
 __global__ void mx_quantize_kernel(const lq_mx_state s, const void* __restrict__ src, int src_dtype, int64_t src_row_stride,
-                                   const lq_rounding rnd, int64_t total_blocks) {
+                                   const lq_rounding rnd, const PhiloxKeys keys, int64_t total_blocks) {
   using IO = MxBlockIO<BITS, LAYOUT>;
   const int nblk = s.dstate / 16;
   const unsigned int* cut = mx_exp_cut_table<BITS>();
+  const MxRoundBase rb = make_round_base(rnd, static_cast<uint64_t>(s.batch) * s.heads * s.dim * s.dstate);
   for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total_blocks;
        t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t row = t / nblk;
@@ -241,9 +462,9 @@ __global__ void mx_quantize_kernel(const lq_mx_state s, const void* __restrict__
 #pragma unroll
     for (int i = 0; i < 16; ++i) hv[i] = load_as_float(src, row * src_row_stride + blk * 16 + i, src_dtype);
     const uint64_t lin = static_cast<uint64_t>(row) * s.dstate + blk * 16;
-    const MxRoundCtx ctx = make_round_ctx<MODE>(rnd, lin, static_cast<uint64_t>(s.batch) * s.heads * s.dim * s.dstate);
+    const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
     uint32_t codes[4], e, mic;
-    mx_encode_block<BITS, MODE>(hv, cut, ctx, codes, e, mic);
+    mx_encode_block<BITS, MODE>(hv, cut, ctx, keys, codes, e, mic);
     IO::store(s, b * s.q_stride[0] + h * s.q_stride[1] + p * s.q_stride[2],
               b * s.exp_stride[0] + h * s.exp_stride[1] + p * s.exp_stride[2],
               b * s.micro_stride[0] + h * s.micro_stride[1] + p * s.micro_stride[2], blk, codes, e, mic);
@@ -323,8 +544,8 @@ static int validate_state(const lq_mx_state& s, const char* who) {
 }
 
 static int validate_rounding(const lq_rounding& r, const char* who) {
-  LQ_CHECK_ARG(r.mode >= LQ_ROUND_HALF_UP && r.mode <= LQ_ROUND_SUPPLIED16, "%s: unknown rounding mode %d", who, r.mode);
-  if (r.mode == LQ_ROUND_SUPPLIED || r.mode == LQ_ROUND_SUPPLIED16) {
+  LQ_CHECK_ARG(r.mode >= LQ_ROUND_HALF_UP && r.mode <= LQ_ROUND_SUPPLIED_FIXED, "%s: unknown rounding mode %d", who, r.mode);
+  if (r.mode == LQ_ROUND_SUPPLIED || r.mode == LQ_ROUND_SUPPLIED_FIXED) {
     LQ_CHECK_ARG(r.words != nullptr, "%s: rounding mode %d needs words", who, r.mode);
     LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(r.words) % 16 == 0, "%s: rounding words must be 16-byte aligned", who);
   }
@@ -333,15 +554,43 @@ static int validate_rounding(const lq_rounding& r, const char* who) {
 }
 
 template <int BITS, int LAYOUT>
+static bool fast_update_applies(const lq_mx_update_args& a, const MxUpdateDerived& d) {
+  using IO = MxBlockIO<BITS, LAYOUT>;
+  const lq_mx_state& s = a.state;
+  const int64_t q_row = static_cast<int64_t>(d.nblk) * IO::kQBytes, m_row = static_cast<int64_t>(d.nblk) * IO::kMicroBytes;
+  const int rows_per_pass = (32 >> d.lpr_log2) * (kUpdateThreads / 32);
+  const bool dense = s.q_stride[2] == q_row && s.q_stride[1] == q_row * s.dim && s.q_stride[0] == q_row * s.dim * s.heads &&
+                     s.exp_stride[2] == d.nblk && s.exp_stride[1] == static_cast<int64_t>(d.nblk) * s.dim &&
+                     s.exp_stride[0] == static_cast<int64_t>(d.nblk) * s.dim * s.heads && s.micro_stride[2] == m_row &&
+                     s.micro_stride[1] == m_row * s.dim && s.micro_stride[0] == m_row * s.dim * s.heads;
+  return dense && d.dt_uniform && d.a_scalar && a.h_out == nullptr && (1 << d.lpr_log2) == d.nblk &&
+         s.dim % rows_per_pass == 0;
+}
+
+template <int BITS, int LAYOUT>
 static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived& d, cudaStream_t st) {
-  const dim3 grid(a.state.batch * a.state.heads), block(kUpdateThreads);
+  if (fast_update_applies<BITS, LAYOUT>(a, d)) {
+    const dim3 grid(a.state.batch * (a.state.heads / d.heads_per_cta)), block(kUpdateThreads);
+    const size_t smem = sizeof(float) * (2 * static_cast<size_t>(d.heads_per_cta) * a.state.dim + 2 * d.heads_per_cta);
+    switch (a.rounding.mode) {
+      case LQ_ROUND_HALF_UP: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, smem, st>>>(a, d); break;
+      case LQ_ROUND_HALF_EVEN: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, smem, st>>>(a, d); break;
+      case LQ_ROUND_PHILOX_REF: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, smem, st>>>(a, d); break;
+      case LQ_ROUND_SUPPLIED: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, smem, st>>>(a, d); break;
+      case LQ_ROUND_PHILOX_LAYERED: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, smem, st>>>(a, d); break;
+      default: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, smem, st>>>(a, d); break;
+    }
+    return;
+  }
+  const dim3 grid(a.state.batch * (a.state.heads / d.heads_per_cta)), block(kUpdateThreads);
+  const size_t smem = sizeof(float) * (2 * static_cast<size_t>(d.heads_per_cta) * a.state.dim + 2 * d.heads_per_cta);
   switch (a.rounding.mode) {
-    case LQ_ROUND_HALF_UP: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, 0, st>>>(a, d); break;
-    case LQ_ROUND_HALF_EVEN: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, 0, st>>>(a, d); break;
-    case LQ_ROUND_PHILOX_REF: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(a, d); break;
-    case LQ_ROUND_SUPPLIED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(a, d); break;
-    case LQ_ROUND_PHILOX_LAYERED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(a, d); break;
-    default: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED16><<<grid, block, 0, st>>>(a, d); break;
+    case LQ_ROUND_HALF_UP: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, smem, st>>>(a, d); break;
+    case LQ_ROUND_HALF_EVEN: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, smem, st>>>(a, d); break;
+    case LQ_ROUND_PHILOX_REF: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, smem, st>>>(a, d); break;
+    case LQ_ROUND_SUPPLIED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, smem, st>>>(a, d); break;
+    case LQ_ROUND_PHILOX_LAYERED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, smem, st>>>(a, d); break;
+    default: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, smem, st>>>(a, d); break;
   }
 }
 
@@ -350,13 +599,14 @@ static void launch_quantize_mode(const lq_mx_state& s, const void* src, int dt, 
                                  int64_t total, cudaStream_t st) {
   const int block = 128;
   const int grid = static_cast<int>(std::min<int64_t>((total + block - 1) / block, 1 << 20));
+  const PhiloxKeys keys = make_philox_keys(r.seed);
   switch (r.mode) {
-    case LQ_ROUND_HALF_UP: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
-    case LQ_ROUND_HALF_EVEN: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
-    case LQ_ROUND_PHILOX_REF: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
-    case LQ_ROUND_SUPPLIED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
-    case LQ_ROUND_PHILOX_LAYERED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
-    default: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED16><<<grid, block, 0, st>>>(s, src, dt, stride, r, total); break;
+    case LQ_ROUND_HALF_UP: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    case LQ_ROUND_HALF_EVEN: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    case LQ_ROUND_PHILOX_REF: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    case LQ_ROUND_SUPPLIED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    case LQ_ROUND_PHILOX_LAYERED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    default: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
   }
 }
 
@@ -389,10 +639,23 @@ LQ_EXPORT int lq_mx_state_update(const lq_mx_update_args* args, void* cuda_strea
   MxUpdateDerived d;
   d.nblk = a.state.dstate / 16;
   if (d.nblk > 32) return fail(LQ_ERR_UNSUPPORTED, "lq_mx_state_update: dstate=%d > 512 is not implemented", a.state.dstate);
+  if (a.state.dim > 4096) return fail(LQ_ERR_UNSUPPORTED, "lq_mx_state_update: dim=%d > 4096 is not implemented", a.state.dim);
   d.lpr_log2 = 0;
   while ((1 << d.lpr_log2) < d.nblk) ++d.lpr_log2;
   d.dt_uniform = (a.dt_stride[2] == 0 && (!a.dt_bias || a.dt_bias_stride[1] == 0)) ? 1 : 0;
   d.a_scalar = (a.A_stride[1] == 0 && a.A_stride[2] == 0) ? 1 : 0;
+  d.keys = make_philox_keys(a.rounding.seed);
+  {
+    // Heads per CTA: as many heads of one B/C group as keeps the grid at >= 4 CTAs per SM (B and C
+    // are then fetched, and dt / exp(A dt) evaluated, once for all of them), and shared memory small.
+    const int per_group = a.state.heads / a.ngroups;
+    const int64_t want_ctas = 4ll * sm_count();
+    int hpc = per_group;
+    while (hpc > 1 && (static_cast<int64_t>(a.state.batch) * (a.state.heads / hpc) < want_ctas || hpc * a.state.dim > 4096 ||
+                       per_group % hpc != 0))
+      --hpc;
+    d.heads_per_cta = hpc;
+  }
   if (a.h_out) LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(a.h_out) % 16 == 0, "lq_mx_state_update: h_out must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 #define LQ_CALL(B_, L_) launch_update_mode<B_, L_>(a, d, st)

@@ -243,7 +243,7 @@ class MxUpdatePlan:
                     or not rand_words.is_contiguous()):
                 raise ValueError(f"rand_words must be a contiguous 32-bit tensor of shape {(batch, nheads, dim, dstate)}")
             r.words = rand_words.data_ptr()
-            r.mode = _lib.LQ_ROUND_SUPPLIED16 if stream == "layered" else _lib.LQ_ROUND_SUPPLIED
+            r.mode = _lib.LQ_ROUND_SUPPLIED_FIXED if stream == "layered" else _lib.LQ_ROUND_SUPPLIED
         elif not stochastic:
             r.mode = _lib.LQ_ROUND_HALF_UP
         elif stream == "reference":

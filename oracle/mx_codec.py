@@ -125,17 +125,16 @@ def mx4_unpack_nibbles(p: np.ndarray) -> np.ndarray:
 
 # ---- the library's own fixed-point stochastic rounding ("layered" Philox stream) --------------
 
-def native_sr_encode(vals: np.ndarray, mantissa_max: int, r16: np.ndarray):
-    """Exponents exactly as :func:`mx_encode`; mantissa by 16-bit fixed-point stochastic
-    rounding: ``t = fl32(v/s + 192)`` clamped to [192-M, 192+M], ``fixed = (t-128) * 2**16``
-    (an integer), ``q = ((fixed + r16) >> 16) - 64`` with ``r16`` uniform in [0, 65535].
-    This has no counterpart in the reference (its stream is one 31-bit draw per value);
-    it defines the library's ``LQ_ROUND_PHILOX_LAYERED`` / ``LQ_ROUND_SUPPLIED16`` modes."""
+def native_sr_encode(vals: np.ndarray, mantissa_max: int, r8: np.ndarray):
+    """Exponents exactly as :func:`mx_encode`; mantissa by fixed-point stochastic rounding with an
+    8-bit uniform draw: ``t = fl32(v/s + 49152 + r8/256)`` (one rounding, as an FMA computes it),
+    ``q = floor(t) - 49152`` with ``r8`` in [0, 255].  This has no counterpart in the reference
+    (its rule is ``floor(a) + (u < frac)`` on a 31-bit uniform ``u``); it defines the library's
+    ``LQ_ROUND_PHILOX_LAYERED`` / ``LQ_ROUND_SUPPLIED_FIXED`` modes."""
     vals = np.asarray(vals, dtype=F32)
     biased, micro, pair_scale = mx_block_scales(vals, mantissa_max)
     scale = np.repeat(pair_scale, 2, axis=-1).astype(np.float64)
-    t = (vals.astype(np.float64) / scale + 192.0).astype(F32)  # one rounding, like an FMA
-    t = np.minimum(np.maximum(t, F32(192 - mantissa_max)), F32(192 + mantissa_max))
-    fixed = np.rint((t.astype(np.float64) - 128.0) * 65536.0).astype(np.int64)
-    q = ((fixed + np.asarray(r16, dtype=np.int64)) >> 16) - 64
+    c = 49152.0 + np.asarray(r8, dtype=np.float64) / 256.0
+    t = (vals.astype(np.float64) / scale + c).astype(F32)  # exact sum in float64, rounded once
+    q = np.floor(t.astype(np.float64)) - 49152.0
     return q.astype(np.int8), biased, micro

@@ -39,30 +39,30 @@ def reference_rng_offsets(step: int, shape) -> np.ndarray:
     return np.uint64(base) + idx
 
 
-def layered_r16(seed: int, layer: int, step: int, shape) -> np.ndarray:
-    """16 random bits per state value for the library's own stream: one Philox4x32-10 block per
-    8 consecutive values, counter = (group_lo, group_hi, step, layer), key = seed; value j of a
-    group takes bits [16*(j&1), 16*(j&1)+16) of word j>>1."""
+def layered_r8(seed: int, layer: int, step: int, shape) -> np.ndarray:
+    """8 random bits per state value for the library's own stream: one Philox4x32-10 block per
+    16-value MX block, counter = (block_lo, block_hi, step, layer), key = seed; value i of a block
+    takes byte i & 3 of word i >> 2."""
     total = int(np.prod(shape))
-    groups = np.arange((total + 7) // 8, dtype=np.uint64)
+    blocks = np.arange((total + 15) // 16, dtype=np.uint64)
     s = int(seed) & 0xFFFFFFFFFFFFFFFF
-    w = philox4x32_10(s & 0xFFFFFFFF, s >> 32, groups & np.uint64(0xFFFFFFFF), groups >> np.uint64(32),
+    w = philox4x32_10(s & 0xFFFFFFFF, s >> 32, blocks & np.uint64(0xFFFFFFFF), blocks >> np.uint64(32),
                       int(step) & 0xFFFFFFFF, int(layer) & 0xFFFFFFFF)
-    words = np.stack(w, axis=-1)  # [groups, 4]
-    halves = np.stack([words & 0xFFFF, words >> 16], axis=-1).reshape(-1)  # [groups*8]
-    return halves[:total].reshape(shape).astype(np.int64)
+    words = np.stack(w, axis=-1).astype(np.uint32)  # [blocks, 4]
+    bytes_ = (words[..., None] >> (np.arange(4, dtype=np.uint32) * 8)) & np.uint32(0xFF)  # [blocks, 4, 4]
+    return bytes_.reshape(-1)[:total].reshape(shape).astype(np.int64)
 
 
 def mx_state_update(q_state, shared_exp, micro_exp, x, dt, A, B, C, D=None, z=None, dt_bias=None,
                     dt_softplus=False, format_bits=8, rounding="stochastic", seed=1234, step=0,
-                    layer=0, rnd=None, r16=None, return_state=False):
+                    layer=0, rnd=None, r8=None, return_state=False):
     """One decode step.  All array arguments are numpy, already broadcast to the shapes the
     reference indexes: q_state int8 [B,H,P,N]; shared_exp uint8 [B,H,P,N/16]; micro_exp uint8
     [B,H,P,N/2]; x, dt, z [B,H,P]; A [H,P,N]; B, C [B,G,N]; D, dt_bias [H,P].
 
     rounding: 'stochastic' (reference Philox stream from seed/step, or ``rnd`` if supplied),
     'half_up' (reference deterministic), 'layered' (library stream from seed/layer/step, or
-    ``r16`` if supplied).
+    ``r8`` if supplied).
     Returns (y fp32 [B,H,P], q', shared_exp', micro_exp') and the fp32 state h' if asked."""
     mmax = 63 if format_bits == 8 else 7
     bsz, nh, dim, dstate = q_state.shape
@@ -87,9 +87,9 @@ def mx_state_update(q_state, shared_exp, micro_exp, x, dt, A, B, C, D=None, z=No
         y = y * np.asarray(z, dtype=F32)  # :163-165
     state = state.astype(F32)
     if rounding == "layered":
-        if r16 is None:
-            r16 = layered_r16(seed, layer, step, state.shape)
-        q, e, m = native_sr_encode(state, mmax, r16)
+        if r8 is None:
+            r8 = layered_r8(seed, layer, step, state.shape)
+        q, e, m = native_sr_encode(state, mmax, r8)
     elif rounding == "stochastic":
         if rnd is None:
             rnd = tl_rand(seed, reference_rng_offsets(step, state.shape))  # :197-198

@@ -77,7 +77,7 @@ def test_argument_validation_needs_no_device(lib):
 def test_workspace_size_and_split_heuristic(lib):
     assert lib.lq_int4_decode_workspace_bytes(0, 32, 8, 128, 4) == 0
     n = lib.lq_int4_decode_workspace_bytes(2, 32, 8, 128, 4)
-    assert n == 256 + 2048 + 2 * 32 * 4 * 128 * 4
+    assert n == 65536 * 4 + 2048 + 2 * 32 * 4 * 128 * 4
     assert lib.lq_int4_decode_auto_splits(1, 8, 1) == 1
     assert lib.lq_int4_decode_auto_splits(1, 8, 64) == 1
     s = lib.lq_int4_decode_auto_splits(1, 8, 131072)

@@ -130,8 +130,10 @@ def test_config0_shape_against_reference_cpu_path():
     v = torch.randn(1, 8, 1024, 128, generator=gen).bfloat16()
     cache = fill_cache(m, k.float().numpy(), v.float().numpy(), 32)
     out = m._decode_attention(q.to(dev()), cache, 1024, 4, 32)
-    kd = m.int4_quant_dequant(k, 32).double().repeat_interleave(4, dim=1)
-    vd = m.int4_quant_dequant(v, 32).double().repeat_interleave(4, dim=1)
+    # fake-quantise in fp32: on bf16 inputs the reference's torch helper rounds the dequantised K/V
+    # back to bf16, which its own fused kernel (and this one) does not do
+    kd = m.int4_quant_dequant(k.float(), 32).double().repeat_interleave(4, dim=1)
+    vd = m.int4_quant_dequant(v.float(), 32).double().repeat_interleave(4, dim=1)
     p = torch.softmax(q.double() @ kd.transpose(-1, -2) / 128 ** 0.5, dim=-1)
     ref = (p @ vd)[:, :, 0].numpy()
     assert out.shape == (1, 32, 128) and out.dtype == torch.bfloat16
@@ -248,3 +250,16 @@ def test_cache_growth_and_errors():
     with pytest.raises(NotImplementedError, match="head_dim=64"):
         c64 = m._allocate_layer_cache(1, 2, 16, 64, 2, dev())
         m._decode_attention(torch.zeros((1, 8, 1, 64), device=dev()), c64, 4, 4, 32)
+
+
+def test_workspace_is_reusable_across_problem_sizes():
+    """The split-merge scratch is shared by every call on a stream: a small problem followed by a
+    larger one (more batch x kv-head tickets, more splits) must still find zeroed tickets."""
+    m = ia()
+    for b, tlen, splits in ((1, 300, 4), (2, 900, 7), (16, 2000, 3), (3, 700, 9), (16, 2000, 16)):
+        k, v = make_kv(b + tlen, b, 8, tlen)
+        q = bf16r(np.random.default_rng(b).standard_normal((b, 32, 1, 128)))
+        cache = fill_cache(m, k, v, 32)
+        ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(cache), tlen, 32)
+        for _ in range(2):
+            assert_out_close(m._decode_attention(t(q), cache, tlen, 4, 32, splits=splits), ref)

@@ -72,14 +72,14 @@ def test_codec_supplied_bits_and_library_stream(golden_dir, bits):
     q, e, m, _ = quantize(vals, bits, "packed", _lib.LQ_ROUND_SUPPLIED, words=words)
     qo, eo, mo = oracle.mx_encode(vals, mmax, "stochastic", oracle.words_to_uniform(words))
     assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(m, mo)
-    # fixed-point rule fed supplied 16-bit draws
-    q, e, m, _ = quantize(vals, bits, "packed", _lib.LQ_ROUND_SUPPLIED16, words=words)
-    qo, eo, mo = oracle.native_sr_encode(vals, mmax, (words & 0xFFFF).astype(np.int64))
+    # fixed-point rule fed supplied 8-bit draws
+    q, e, m, _ = quantize(vals, bits, "packed", _lib.LQ_ROUND_SUPPLIED_FIXED, words=words)
+    qo, eo, mo = oracle.native_sr_encode(vals, mmax, (words & 0xFF).astype(np.int64))
     assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(m, mo)
     # library Philox stream keyed on (seed, layer, step, index)
-    from oracle.mx_state import layered_r16
+    from oracle.mx_state import layered_r8
     q, e, m, _ = quantize(vals, bits, "reference", _lib.LQ_ROUND_PHILOX_LAYERED, seed=77, layer=5, step=9)
-    qo, eo, mo = oracle.native_sr_encode(vals, mmax, layered_r16(77, 5, 9, vals.shape))
+    qo, eo, mo = oracle.native_sr_encode(vals, mmax, layered_r8(77, 5, 9, vals.shape))
     assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(m, mo)
     # 64-bit reference counters (RNG_OFFSET >= 2**32 keeps both words, below it wraps to 32 bits)
     for off in (2**32 - 1000, 2**32 + 12345, 2**31 - 5):
@@ -203,7 +203,7 @@ def test_fused_update_shapes_and_supplied_bits(case, bits):
         if stream == "reference":
             qo, eo, mo = oracle.mx_encode(hh, mmax, "stochastic", oracle.words_to_uniform(words[0]))
         else:
-            qo, eo, mo = oracle.native_sr_encode(hh, mmax, (words[0] & 0xFFFF).astype(np.int64))
+            qo, eo, mo = oracle.native_sr_encode(hh, mmax, (words[0] & 0xFF).astype(np.int64))
         assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(mi, mo)
 
 
@@ -303,3 +303,30 @@ def test_errors_match_reference_behaviour():
         m.mx_state_selective_update(cache, x, x, x, x, x)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         m.allocate_state_kernel_cache(st.cpu())
+
+
+@pytest.mark.parametrize("bits,layout", [(8, "packed"), (8, "reference"), (4, "packed"), (4, "reference")])
+def test_dense_fast_path_equals_general_kernel(bits, layout):
+    """The dense fast-path kernel (taken when no fp32 state dump is requested and the shape is the
+    regular decode shape) and the general kernel must agree bit for bit, in every rounding mode."""
+    m = mk()
+    b, h, p, n, g = 3, 16, 64, 128, 2
+    d = make_update_case(31, b, h, p, n, g, with_z=True)
+    x, dt, A, B, C, D, z, bias = expand_update_operands(d)
+    rng = np.random.default_rng(32)
+    words = t(rng.integers(0, 2**32, size=(b, h, p, n), dtype=np.uint64).astype(np.uint32).view(np.int32))
+    for kw in (dict(stochastic=False), dict(stochastic=True, seed=5), dict(stochastic=True, seed=5, rng_stream="layered"),
+               dict(rand_words=words), dict(rand_words=words, rng_stream="layered")):
+        res = []
+        for use_dump in (False, True):
+            cache = m.allocate_state_kernel_cache(t(d["state"]), 16, bits, layout=layout)
+            cache.layer, cache.step = 3, 2
+            extra = dict(h_out=torch.empty((b, h, p, n), dtype=torch.float32, device=dev())) if use_dump else {}
+            ys = [m.mx_state_selective_update(cache, x, dt, A, B, C, D=D, z=z, dt_bias=bias, dt_softplus=True, **kw, **extra).clone()
+                  for _ in range(2)]
+            res.append((ys, cache))
+        (y_fast, c_fast), (y_gen, c_gen) = res
+        for ya, yb in zip(y_fast, y_gen):
+            assert torch.equal(ya, yb), kw
+        assert torch.equal(c_fast.q_state, c_gen.q_state) and torch.equal(c_fast.shared_exp, c_gen.shared_exp), kw
+        assert torch.equal(c_fast.micro_exp, c_gen.micro_exp), kw
