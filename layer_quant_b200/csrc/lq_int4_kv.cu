@@ -36,7 +36,7 @@ constexpr int kHeadDim = 128;
 constexpr int kTile = 64;           // tokens per ring stage
 constexpr int kStages = 4;
 constexpr int kConsumerWarps = 8;
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
+constexpr int kDecodeThreads = kConsumerWarps * 32;  // thread 0 doubles as the copy producer
 constexpr int kTokPerWarp = kTile / kConsumerWarps;  // 8 tokens = 2 passes of 4
 constexpr uint32_t kWaitLimit = 1u << 22;            // polls before a wait gives up
 
@@ -206,7 +206,12 @@ struct StageLayout {
   static constexpr int kNewRowBytes = 2 * (kHeadDim / 2) + 2 * 16 * 4;
 };
 
-__device__ __forceinline__ float exp2_or_zero(float m, float m_new) { return m == -INFINITY ? 0.0f : exp2f(m - m_new); }
+// Running maxima start at kNegBig instead of -inf: exp2(kNegBig - m) is 0 for any finite m, and no
+// inf - inf can appear.  A stream that saw no unmasked token keeps (kNegBig, 0, 0).
+constexpr float kNegBig = -1.0e30f;
+// The running maximum is only raised when a score exceeds it by more than this (log2 units), so
+// probabilities stay below 2^8 and the output rescale is rare and taken by the whole warp at once.
+constexpr float kRescaleSlack = 8.0f;
 
 // 16 nibbles (two 32-bit words) -> 16 floats 136 + n
 __device__ __forceinline__ void unpack16(uint2 c, float (&f)[16]) {
@@ -297,7 +302,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   float m_run[R], l_run[R], psum[R];
   float acc[R][16];
   const float scale_sm = 1.4426950408889634f / sqrtf(static_cast<float>(kHeadDim));
-  if (warp < kConsumerWarps) {
+  {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float s = 0.0f;
@@ -309,7 +314,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
         acc[r][i] = 0.0f;
       }
       qcorr[r] = -136.0f * s;
-      m_run[r] = -INFINITY;
+      m_run[r] = kNegBig;
       l_run[r] = 0.0f;
       psum[r] = 0.0f;
     }
@@ -337,18 +342,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
     }
     if (!valid) return;
     unpack16(vc, f);
+    bool grow = false;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const float sr = HAS_MASK ? s[r] + bias : s[r];
-      if (sr > m_run[r]) {  // rare after the first tokens: rescale this head's running state
-        const float alpha = exp2_or_zero(m_run[r], sr);
+      if (HAS_MASK) s[r] += bias;
+      grow |= s[r] > m_run[r] + kRescaleSlack;
+    }
+    if (grow) {  // rare: raise the running maxima and rescale the running sums
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float m_new = fmaxf(m_run[r], s[r]);
+        const float alpha = exp2f(m_run[r] - m_new);
         l_run[r] *= alpha;
         psum[r] *= alpha;
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[r][i] *= alpha;
-        m_run[r] = sr;
+        m_run[r] = m_new;
       }
-      const float pr = (sr == -INFINITY) ? 0.0f : exp2f(sr - m_run[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float pr = exp2f(s[r] - m_run[r]);
       l_run[r] += pr;
       const float pv = pr * vsc;
       psum[r] += pv;
@@ -362,49 +376,40 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   const int64_t ks_base = b * c.ks_stride[0] + kvh * c.ks_stride[1];
   const int64_t vs_base = b * c.vs_stride[0] + kvh * c.vs_stride[1];
 
-  if (warp == kConsumerWarps) {
-    // ---- producer: one lane streams the tiles ----
-    if (lane == 0) {
-      int issued = 0;
-      for (int it = 0; it < my_tiles; ++it) {
-        const int st = it % kStages;
-        if (it >= kStages && !mbar_wait(&bar_empty[st], ((it / kStages) - 1) & 1, &s_abort)) break;
-        const int tok0 = (tile_begin + it) * kTile;
-        const int rows = min(kTile, p.ctx_len - tok0);
-        const uint32_t code_bytes = rows * (kHeadDim / 2);
-        const uint32_t scale_bytes = rows * G * 4;
-        const uint32_t scale_bulk = scale_bytes & ~15u;
-        uint8_t* stage = smem + st * L::kBytes;
-        const float* ks_src = c.k_scale + ks_base + static_cast<int64_t>(tok0) * G;
-        const float* vs_src = c.v_scale + vs_base + static_cast<int64_t>(tok0) * G;
-        // a ragged last tile can leave < 16 bytes of scales that a bulk copy cannot carry
-        for (uint32_t o = scale_bulk; o < scale_bytes; o += 4) {
-          *reinterpret_cast<float*>(stage + L::kKs + o) = ks_src[o / 4];
-          *reinterpret_cast<float*>(stage + L::kVs + o) = vs_src[o / 4];
-        }
-        mbar_arrive_expect_tx(&bar_full[st], 2 * code_bytes + 2 * scale_bulk);
-        bulk_copy_g2s(stage + L::kKc, c.k_packed + kp_base + static_cast<int64_t>(tok0) * (kHeadDim / 2), code_bytes, &bar_full[st]);
-        bulk_copy_g2s(stage + L::kVc, c.v_packed + vp_base + static_cast<int64_t>(tok0) * (kHeadDim / 2), code_bytes, &bar_full[st]);
-        if (scale_bulk) {
-          bulk_copy_g2s(stage + L::kKs, ks_src, scale_bulk, &bar_full[st]);
-          bulk_copy_g2s(stage + L::kVs, vs_src, scale_bulk, &bar_full[st]);
-        }
-        issued = it + 1;
-      }
-      // after an abort, let copies still in flight land before the CTA's shared memory goes away
-      if (s_abort) {
-        for (int it = max(0, issued - kStages); it < issued; ++it) {
-          const int st = it % kStages;
-          for (uint32_t i = 0; i < kWaitLimit && !mbar_try_wait(&bar_full[st], (it / kStages) & 1); ++i) {
-          }
-        }
-      }
+  // Thread 0 is also the copy producer: it fills the ring ahead of the consumers and, after its warp
+  // has finished a tile, refills that stage as soon as every warp has released it.
+  auto issue_tile = [&](int it) {
+    const int st = it % kStages;
+    const int tok0 = (tile_begin + it) * kTile;
+    const int rows = min(kTile, p.ctx_len - tok0);
+    const uint32_t code_bytes = rows * (kHeadDim / 2);
+    const uint32_t scale_bytes = rows * G * 4;
+    const uint32_t scale_bulk = scale_bytes & ~15u;
+    uint8_t* stage = smem + st * L::kBytes;
+    const float* ks_src = c.k_scale + ks_base + static_cast<int64_t>(tok0) * G;
+    const float* vs_src = c.v_scale + vs_base + static_cast<int64_t>(tok0) * G;
+    // a ragged last tile can leave < 16 bytes of scales that a bulk copy cannot carry
+    for (uint32_t o = scale_bulk; o < scale_bytes; o += 4) {
+      *reinterpret_cast<float*>(stage + L::kKs + o) = ks_src[o / 4];
+      *reinterpret_cast<float*>(stage + L::kVs + o) = vs_src[o / 4];
     }
-  } else {
-    // ---- consumers ----
+    mbar_arrive_expect_tx(&bar_full[st], 2 * code_bytes + 2 * scale_bulk);
+    bulk_copy_g2s(stage + L::kKc, c.k_packed + kp_base + static_cast<int64_t>(tok0) * (kHeadDim / 2), code_bytes, &bar_full[st]);
+    bulk_copy_g2s(stage + L::kVc, c.v_packed + vp_base + static_cast<int64_t>(tok0) * (kHeadDim / 2), code_bytes, &bar_full[st]);
+    if (scale_bulk) {
+      bulk_copy_g2s(stage + L::kKs, ks_src, scale_bulk, &bar_full[st]);
+      bulk_copy_g2s(stage + L::kVs, vs_src, scale_bulk, &bar_full[st]);
+    }
+  };
+  int issued = 0, consumed = 0;  // meaningful in thread 0
+  if (threadIdx.x == 0) {
+    for (; issued < min(kStages, my_tiles); ++issued) issue_tile(issued);
+  }
+  {
     for (int it = 0; it < my_tiles; ++it) {
       const int st = it % kStages;
       if (!mbar_wait(&bar_full[st], (it / kStages) & 1, &s_abort)) break;
+      consumed = it + 1;
       const uint8_t* stage = smem + st * L::kBytes;
       const int tok0 = (tile_begin + it) * kTile;
       const int rows = min(kTile, p.ctx_len - tok0);
@@ -429,6 +434,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
       for (int ps = 0; ps < 2; ++ps) process_token(tl[ps] < rows, kc[ps], vc[ps], ksc[ps], vsc[ps], bias[ps]);
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_empty[st]);
+      if (threadIdx.x == 0 && issued < my_tiles) {
+        if (!mbar_wait(&bar_empty[st], (it / kStages) & 1, &s_abort)) break;
+        issue_tile(issued);
+        ++issued;
+      }
+    }
+    // after an abort, let copies still in flight land before the CTA's shared memory goes away
+    if (threadIdx.x == 0 && s_abort) {
+      for (int it = consumed; it < issued; ++it) {
+        const int st = it % kStages;
+        for (uint32_t i = 0; i < kWaitLimit && !mbar_try_wait(&bar_full[st], (it / kStages) & 1); ++i) {
+        }
+      }
     }
     if (do_new) {  // the row appended in this step, read back from shared memory by one 8-lane group
       const uint2 kc = *reinterpret_cast<const uint2*>(newrow + sub * 8);
@@ -455,7 +473,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
         const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m_run[r], o);
         const float l_o = __shfl_xor_sync(0xFFFFFFFFu, l_run[r], o);
         const float m_n = fmaxf(m_run[r], m_o);
-        const float fa = exp2_or_zero(m_run[r], m_n), fb = exp2_or_zero(m_o, m_n);
+        const float fa = exp2f(m_run[r] - m_n), fb = exp2f(m_o - m_n);
         l_run[r] = l_run[r] * fa + l_o * fb;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -468,7 +486,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   }
   __syncthreads();  // every bulk copy has been consumed (or drained): the ring can be reused
   float* s_acc = reinterpret_cast<float*>(smem);  // [warps][R][128]
-  if (warp < kConsumerWarps && tg == 0) {
+  if (tg == 0) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float4* dst = reinterpret_cast<float4*>(s_acc + (warp * R + r) * kHeadDim + sub * 16);
@@ -486,13 +504,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   const int hq0 = kvh * R;
   for (int o = threadIdx.x; o < R * kHeadDim; o += kDecodeThreads) {
     const int r = o / kHeadDim, d = o - r * kHeadDim;
-    float M = -INFINITY;
+    float M = kNegBig;
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, s_m[w][r]);
     float Lsum = 0.0f, O = 0.0f;
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; ++w) {
-      const float fct = exp2_or_zero(s_m[w][r], M);
+      const float fct = exp2f(s_m[w][r] - M);
       Lsum = fmaf(s_l[w][r], fct, Lsum);
       O = fmaf(s_acc[(w * R + r) * kHeadDim + d], fct, O);
     }
@@ -522,11 +540,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   for (int o = threadIdx.x; o < R * kHeadDim; o += kDecodeThreads) {
     const int r = o / kHeadDim, d = o - r * kHeadDim;
     const int64_t slot0 = (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits;
-    float M = -INFINITY;
+    float M = kNegBig;
     for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slot0 + s) * 2));
     float Lsum = 0.0f, O = 0.0f;
     for (int s = 0; s < p.splits; ++s) {
-      const float fct = exp2_or_zero(__ldcg(p.part_ml + (slot0 + s) * 2), M);
+      const float fct = exp2f(__ldcg(p.part_ml + (slot0 + s) * 2) - M);
       Lsum = fmaf(__ldcg(p.part_ml + (slot0 + s) * 2 + 1), fct, Lsum);
       O = fmaf(__ldcg(p.part_acc + (slot0 + s) * kHeadDim + d), fct, O);
     }
