@@ -197,6 +197,27 @@ size_t lq_int4_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv
 /* The split count the library would pick for this problem on the current device (>= 1). */
 int32_t lq_int4_decode_auto_splits(int32_t batch, int32_t kv_heads, int32_t seq_len);
 
+/* lq_int4_decode_attn for callers that cannot hand over scratch memory of their own: a process
+ * whose memory pool has already taken all of the device memory (a cudaMalloc would fail), or a
+ * latency-critical thread that must not take the device-wide lock an allocation takes.  Same
+ * arguments and results as lq_int4_decode_attn, except that args->workspace / workspace_bytes are
+ * ignored: the split-merge scratch is an array built into the library image
+ * (lq_int4_static_scratch_bytes() bytes, about 4.4 MB, held by every GPU that loads the library
+ * until the process exits).  This entry point has no counterpart in the reference.
+ *   - Limit: batch * q_heads * splits <= LQ_INT4_STATIC_MAX_SLOTS.  With splits = 0 the library
+ *     picks a split count inside the limit; an explicit splits beyond it is refused with
+ *     LQ_ERR_WORKSPACE.  One split needs no scratch and is always accepted.
+ *   - It allocates nothing (no cudaMalloc / cudaFree / allocating library call).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which still holds the previous call's contents;
+ *     the ticket counters are cleared on the stream before each launch.  Two calls that may overlap
+ *     on the GPU (different streams) race on it: serialise them, or use lq_int4_decode_attn with
+ *     one workspace per stream.                                                                 */
+#define LQ_INT4_STATIC_MAX_SLOTS 8192
+int lq_int4_decode_attn_static(const lq_int4_decode_args* args, void* cuda_stream);
+size_t lq_int4_static_scratch_bytes(void);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Library                                                                                    */
 /* ------------------------------------------------------------------------------------------ */

@@ -105,6 +105,8 @@ def lib() -> C.CDLL:
     l.lq_int4_kv_append.argtypes = [C.POINTER(Int4Cache), C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                                     C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
     l.lq_int4_decode_attn.argtypes = [C.POINTER(Int4DecodeArgs), C.c_void_p]
+    l.lq_int4_decode_attn_static.argtypes = [C.POINTER(Int4DecodeArgs), C.c_void_p]
+    l.lq_int4_static_scratch_bytes.restype = C.c_size_t
     l.lq_int4_decode_workspace_bytes.argtypes = [C.c_int32] * 5
     l.lq_int4_decode_workspace_bytes.restype = C.c_size_t
     l.lq_int4_decode_auto_splits.argtypes = [C.c_int32] * 3

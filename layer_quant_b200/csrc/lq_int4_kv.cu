@@ -736,3 +736,64 @@ LQ_EXPORT int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_st
       return fail(LQ_ERR_UNSUPPORTED, "lq_int4_decode_attn: %d query heads per kv head (supported: 1, 2, 4, 8)", a.q_heads / c.kv_heads);
   }
 }
+
+// ---- decode attention with built-in scratch --------------------------------------------------------
+// Scratch for lq_int4_decode_attn_static: lives in the library image, so every GPU that loads the
+// library holds these bytes until the process exits.  Layout = the ordinary workspace layout (ticket
+// region first), sized for LQ_INT4_STATIC_MAX_SLOTS partial results of 128 dimensions.
+namespace lq {
+constexpr size_t kStaticScratchBytes =
+    kTicketBytes + LQ_INT4_STATIC_MAX_SLOTS * 2 * sizeof(float) + LQ_INT4_STATIC_MAX_SLOTS * kHeadDim * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// The array's name is only a host-side handle; the device address has to be asked for, per device.
+static int static_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  LQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(LQ_ERR_UNSUPPORTED, "lq_int4_decode_attn_static: device index %d out of range", dev);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    LQ_CHECK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (p == nullptr) return fail(LQ_ERR_CUDA, "lq_int4_decode_attn_static: no device address for the built-in scratch");
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return LQ_OK;
+}
+}  // namespace lq
+
+LQ_EXPORT size_t lq_int4_static_scratch_bytes(void) { return lq::kStaticScratchBytes; }
+
+LQ_EXPORT int lq_int4_decode_attn_static(const lq_int4_decode_args* args, void* cuda_stream) {
+  LQ_CHECK_ARG(args != nullptr, "lq_int4_decode_attn_static: null args");
+  lq_int4_decode_args a = *args;
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  const lq_int4_cache& c = a.cache;
+  LQ_CHECK_ARG(c.batch > 0 && c.kv_heads > 0 && a.q_heads > 0 && a.seq_len >= 1, "lq_int4_decode_attn_static: empty problem");
+  const int64_t per_split = static_cast<int64_t>(c.batch) * a.q_heads;
+  const int64_t max_splits = static_cast<int64_t>(LQ_INT4_STATIC_MAX_SLOTS) / per_split;
+  int splits = a.splits;
+  if (splits <= 0) {  // library's choice, kept inside what the built-in scratch can hold
+    splits = pick_splits(c.batch, c.kv_heads, std::max(a.seq_len - (a.k_new ? 1 : 0), 1));
+    if (splits > max_splits) splits = static_cast<int>(std::max<int64_t>(max_splits, 1));
+  } else if (splits > 1 && splits > max_splits) {
+    return fail(LQ_ERR_WORKSPACE,
+                "lq_int4_decode_attn_static: batch %d x %d query heads x %d splits = %lld partial results exceed the built-in "
+                "scratch (%d); use fewer splits or lq_int4_decode_attn with a caller-provided workspace",
+                c.batch, a.q_heads, splits, (long long)(per_split * splits), LQ_INT4_STATIC_MAX_SLOTS);
+  }
+  if (splits > 1 && static_cast<size_t>(c.batch) * c.kv_heads > kMaxTickets)
+    return fail(LQ_ERR_WORKSPACE, "lq_int4_decode_attn_static: batch x kv heads = %lld exceeds %zu tickets",
+                (long long)c.batch * c.kv_heads, kMaxTickets);
+  a.splits = splits;
+  a.workspace = scratch;
+  a.workspace_bytes = kStaticScratchBytes;
+  if (splits > 1) {
+    // every call shares the array and finds what the last call left: tickets must start at zero
+    LQ_CHECK_CUDA(cudaMemsetAsync(scratch, 0, static_cast<size_t>(c.batch) * c.kv_heads * sizeof(int32_t),
+                                  static_cast<cudaStream_t>(cuda_stream)));
+  }
+  return lq_int4_decode_attn(&a, cuda_stream);
+}
