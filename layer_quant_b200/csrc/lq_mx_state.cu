@@ -12,6 +12,7 @@
 // written the memory system could deliver one value every ~12 issue slots per SM sub-partition,
 // and decode + update + read-out + exponent + rounding + random bits need more than that.
 #include <algorithm>
+#include <cstdlib>
 
 #include "lq_mx_codec.cuh"
 
@@ -157,6 +158,7 @@ struct MxUpdateDerived {
   int32_t a_scalar;    // A depends on the head only
   int32_t heads_per_cta;  // consecutive heads of one B/C group handled by one CTA
   PhiloxKeys keys;        // round keys of rounding.seed
+  uint64_t units_total;   // fast path: batch * heads * dim / rows per pass
 };
 
 __device__ __forceinline__ float softplus_ref(float x) { return x <= 20.0f ? logf(1.0f + expf(x)) : x; }
@@ -276,19 +278,21 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
         mx_decode_block(codes, cur.e, cur.mic, hv);
         const float xv = sxh[p];
         if (hoisted) {
+          const float dtx = dt_h * xv;  // h' = h exp(A dt) + B (dt x)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + (Bv[i] * dt_h) * xv;  // (B dt) x: the reference's order
+          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
         } else {
           const float dt = d.dt_uniform ? dt_h : row_dt(h, p);
+          const float dtx = dt * xv;
           if (d.a_scalar) {
             const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + (Bv[i] * dt) * xv;
+            for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + Bv[i] * dtx;
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
-              hv[i] = hv[i] * expf(Ai * dt) + (Bv[i] * dt) * xv;
+              hv[i] = hv[i] * expf(Ai * dt) + Bv[i] * dtx;
             }
           }
         }
@@ -333,84 +337,109 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
 
 // Fast path of the fused update: the shape every Mamba2 decode step has.  Requirements (checked
 // on the host): dense state tensors, dt / dt_bias / A per head only, dstate / 16 a power of two,
-// dim a multiple of the rows one CTA pass covers, no h_out.  Every lane is then always active, all
-// addresses are one per-CTA 64-bit base plus 32-bit offsets bumped by a constant, and the loop body
-// has no divergent branch.
-template <int BITS, int LAYOUT, int MODE>
+// dim a multiple of the rows one CTA pass covers, no h_out.
+//
+// Work is cut into units of `rows_per_pass` consecutive rows (one pass of the CTA's four warps).
+// Units are numbered in memory order, so CTA c owns units [c U / G, (c + 1) U / G): a contiguous
+// slab of the state, balanced to within one unit whatever the batch, and the grid is one wave of
+// resident CTAs whenever the slab's x / y staging fits in shared memory.  Every lane is always
+// active, the three state pointers move by a constant per pass (also across head boundaries), and
+// B / C are reloaded only when the slab crosses into another (batch, B/C group).
+// NBLK_T = dstate / 16 when known at compile time (8 for Nemotron-H: all lane and address arithmetic
+// folds to constants and the read-out reduction unrolls), 0 = taken from the arguments.
+template <int BITS, int LAYOUT, int MODE, int NBLK_T>
 __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
   using IO = MxBlockIO<BITS, LAYOUT>;
   extern __shared__ float smem_xy[];
   const lq_mx_state& s = a.state;
   const int H = s.heads, P = s.dim;
-  const int hpc = d.heads_per_cta;
-  float* sx = smem_xy;
-  float* sy = sx + hpc * P;
-  float* sdt = sy + hpc * P;
-  float* sdA = sdt + hpc;
-  const int chunks = H / hpc;
-  const int b = blockIdx.x / chunks;
-  const int h0 = (blockIdx.x - b * chunks) * hpc;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int blk = lane & (d.nblk - 1);
-  const int rsub = lane >> d.lpr_log2;
-  const int rows_per_warp = 32 >> d.lpr_log2;
+  const int nblk = NBLK_T ? NBLK_T : d.nblk;
+  const int lpr_log2 = NBLK_T == 8 ? 3 : d.lpr_log2;
+  const int dstate = NBLK_T ? NBLK_T * 16 : s.dstate;
+  const int blk = lane & (nblk - 1);
+  const int rsub = lane >> lpr_log2;
+  const int rows_per_warp = 32 >> lpr_log2;
   const int rows_per_pass = rows_per_warp * (kUpdateThreads / 32);
+  const int units_per_head = P / rows_per_pass;
+  const int heads_per_group = H / a.ngroups;
   const int n0 = blk * 16;
-  const int grp = h0 / (H / a.ngroups);
   const unsigned int* cut = mx_exp_cut_table<BITS>();
 
-  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
-    const int hh = i / P, p = i - hh * P;
-    sx[i] = load_as_float(a.x, b * a.x_stride[0] + (h0 + hh) * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
+  // this CTA's slab: units [u0, u1), rows [R0, R1) of the [batch * heads * dim] row space
+  const uint64_t u0 = static_cast<uint64_t>(blockIdx.x) * d.units_total / gridDim.x;
+  const uint64_t u1 = static_cast<uint64_t>(blockIdx.x + 1) * d.units_total / gridDim.x;
+  const int n_units = static_cast<int>(u1 - u0);
+  if (n_units == 0) return;
+  const uint64_t R0 = u0 * rows_per_pass;
+  const int n_rows = n_units * rows_per_pass;
+  const uint64_t bh_first = u0 / units_per_head;                 // first (batch * heads + head) index touched
+  const int n_heads = static_cast<int>((u1 - 1) / units_per_head - bh_first) + 1;
+  float* sx = smem_xy;        // x, later y, of the slab's rows
+  float* sy = sx + n_rows;
+  float* sdt = sy + n_rows;   // per touched head
+  float* sdA = sdt + n_heads;
+
+  for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
+    const uint64_t R = R0 + i;
+    const int p = static_cast<int>(R % P);
+    const uint64_t bh = R / P;
+    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+    sx[i] = load_as_float(a.x, b * a.x_stride[0] + h * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
   }
-  if (threadIdx.x < hpc) {
-    const int h = h0 + threadIdx.x;
+  for (int i = threadIdx.x; i < n_heads; i += kUpdateThreads) {
+    const uint64_t bh = bh_first + i;
+    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
     float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1], a.dt_dtype);
     if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0], a.dt_bias_dtype);
     if (a.dt_softplus) dt = softplus_ref(dt);
-    sdt[threadIdx.x] = dt;
-    sdA[threadIdx.x] = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
+    sdt[i] = dt;
+    sdA[i] = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
   }
+  // position of the first unit: head index inside the slab, unit inside the head, head inside its group
+  int head_i = 0;
+  int unit_in_head = static_cast<int>(u0 % units_per_head);
+  int h_cur = static_cast<int>(bh_first % H);
+  int b_cur = static_cast<int>(bh_first / H);
   float Bv[16], Cv[16];
-  load_bc16(a.B, a.B_stride, a.B_dtype, b, grp, n0, Bv);
-  load_bc16(a.C, a.C_stride, a.C_dtype, b, grp, n0, Cv);
-  const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * s.dstate);
+  load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, h_cur / heads_per_group, n0, Bv);
+  load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
+  const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * dstate);
 
-  // dense addressing: row r of the CTA (r in [0, hpc * P)), block blk
-  const uint32_t q_row = d.nblk * IO::kQBytes, m_row = d.nblk * IO::kMicroBytes, e_row = d.nblk;
-  const uint64_t row0 = (static_cast<uint64_t>(b) * H + h0) * P;
-  uint8_t* const qp = static_cast<uint8_t*>(s.q_state) + row0 * q_row;
-  uint8_t* const ep = s.shared_exp + row0 * e_row;
-  uint8_t* const mp = s.micro_exp + row0 * m_row;
-  const uint64_t lin0 = row0 * s.dstate;  // linear index of the CTA's first value
+  const uint32_t q_row = nblk * IO::kQBytes, m_row = nblk * IO::kMicroBytes, e_row = nblk;
   const uint32_t r_first = warp * rows_per_warp + rsub;
-  uint32_t qoff = r_first * q_row + blk * IO::kQBytes;
-  uint32_t eoff = r_first * e_row + blk;
-  uint32_t moff = r_first * m_row + blk * IO::kMicroBytes;
-  uint32_t loff = r_first * s.dstate + n0;  // value offset inside the CTA's rows (< 2^32: hpc * P * dstate)
+  // this lane's block of its first row; every pass moves all three pointers by a constant
+  uint8_t* qptr = static_cast<uint8_t*>(s.q_state) + (R0 + r_first) * q_row + blk * IO::kQBytes;
+  uint8_t* eptr = s.shared_exp + (R0 + r_first) * e_row + blk;
+  uint8_t* mptr = s.micro_exp + (R0 + r_first) * m_row + blk * IO::kMicroBytes;
+  uint64_t lin = (R0 + r_first) * dstate + n0;
   uint32_t row = r_first;
   const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
-                 dl = rows_per_pass * s.dstate;
-  const int iters_per_head = P / rows_per_pass;
+                 dl = rows_per_pass * dstate;
   __syncthreads();
 
-  MxRaw cur = IO::load_ptr(qp + qoff, ep + eoff, mp + moff);
+  MxRaw cur = IO::load_ptr(qptr, eptr, mptr);
+  int u = 0;
 #pragma unroll 1
-  for (int hh = 0; hh < hpc; ++hh) {
-    const float dt_h = sdt[hh], dA_h = sdA[hh];
-    const bool last_head = hh + 1 == hpc;
+  while (u < n_units) {
+    // units of one head
+    const float dt_h = sdt[head_i], dA_h = sdA[head_i];
+    const int u_head_end = min(n_units, u + units_per_head - unit_in_head);
 #pragma unroll 1
-    for (int it = 0; it < iters_per_head; ++it) {
+    for (; u < u_head_end; ++u) {
+      uint8_t* const qn = qptr + dq;
+      uint8_t* const en = eptr + de;
+      uint8_t* const mn = mptr + dm;
       MxRaw nxt = cur;
-      if (!(last_head && it + 1 == iters_per_head)) nxt = IO::load_ptr(qp + qoff + dq, ep + eoff + de, mp + moff + dm);
+      if (u + 1 < n_units) nxt = IO::load_ptr(qn, en, mn);
 
       uint32_t codes[4];
       IO::codes_of(cur, codes);
       float hv[16];
       mx_decode_block(codes, cur.e, cur.mic, hv);
-      const float xv = sx[row];
+      const float dtx = dt_h * sx[row];  // h' = h exp(A dt) + B (dt x)
 #pragma unroll
-      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + (Bv[i] * dt_h) * xv;  // (B dt) x: the reference's order
+      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
       float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
@@ -421,20 +450,46 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
       }
       float y = (y0 + y1) + (y2 + y3);
 
-      const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin0 + loff);
+      const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
       uint32_t e_new, mic_new;
       mx_encode_block<BITS, MODE>(hv, cut, ctx, d.keys, codes, e_new, mic_new);
-      IO::store_ptr(qp + qoff, ep + eoff, mp + moff, codes, e_new, mic_new);
+      IO::store_ptr(qptr, eptr, mptr, codes, e_new, mic_new);
 
-      for (int o = d.nblk >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+      if (NBLK_T == 8) {
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+      } else {
+        for (int o = nblk >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+      }
       if (blk == 0) sy[row] = y;
       cur = nxt;
-      qoff += dq; eoff += de; moff += dm; loff += dl; row += rows_per_pass;
+      qptr = qn; eptr = en; mptr = mn;
+      lin += dl;
+      row += rows_per_pass;
+    }
+    // the next unit, if any, starts another head; B / C change only with the (batch, group)
+    unit_in_head = 0;
+    ++head_i;
+    if (u < n_units) {
+      const int g_old = h_cur / heads_per_group;
+      if (++h_cur == H) {
+        h_cur = 0;
+        ++b_cur;
+      }
+      if (h_cur / heads_per_group != g_old || h_cur == 0) {
+        load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, h_cur / heads_per_group, n0, Bv);
+        load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
+      }
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < hpc * P; i += kUpdateThreads) {
-    const int hh = i / P, p = i - hh * P, h = h0 + hh;
+  // y = <h', C> + D x (* z), stored for the whole slab at once
+  for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
+    const uint64_t R = R0 + i;
+    const int p = static_cast<int>(R % P);
+    const uint64_t bh = R / P;
+    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
     float y = sy[i];
     if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
     if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
@@ -570,16 +625,38 @@ static bool fast_update_applies(const lq_mx_update_args& a, const MxUpdateDerive
 template <int BITS, int LAYOUT>
 static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived& d, cudaStream_t st) {
   if (fast_update_applies<BITS, LAYOUT>(a, d)) {
-    const dim3 grid(a.state.batch * (a.state.heads / d.heads_per_cta)), block(kUpdateThreads);
-    const size_t smem = sizeof(float) * (2 * static_cast<size_t>(d.heads_per_cta) * a.state.dim + 2 * d.heads_per_cta);
-    switch (a.rounding.mode) {
-      case LQ_ROUND_HALF_UP: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_HALF_UP><<<grid, block, smem, st>>>(a, d); break;
-      case LQ_ROUND_HALF_EVEN: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_HALF_EVEN><<<grid, block, smem, st>>>(a, d); break;
-      case LQ_ROUND_PHILOX_REF: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, smem, st>>>(a, d); break;
-      case LQ_ROUND_SUPPLIED: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, smem, st>>>(a, d); break;
-      case LQ_ROUND_PHILOX_LAYERED: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, smem, st>>>(a, d); break;
-      default: mx_state_update_fast_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, smem, st>>>(a, d); break;
+    // One wave of resident CTAs (4 per SM) when a CTA's slab stays within kMaxUnitsPerCta units
+    // (its x / y staging in shared memory); more waves of equally sized slabs otherwise.
+    uint64_t kMaxUnitsPerCta = 64;
+    if (const char* env = getenv("LQ_MX_MAX_UNITS")) kMaxUnitsPerCta = std::max(1, atoi(env));  // tuning aid
+    const int rows_per_pass = (32 >> d.lpr_log2) * (kUpdateThreads / 32);
+    MxUpdateDerived dd = d;
+    dd.units_total = static_cast<uint64_t>(a.state.batch) * a.state.heads * (a.state.dim / rows_per_pass);
+    const uint64_t wave = 4ull * sm_count();
+    uint64_t ctas = std::min<uint64_t>(dd.units_total, wave);
+    if (dd.units_total > ctas * kMaxUnitsPerCta) {
+      ctas = (dd.units_total + kMaxUnitsPerCta - 1) / kMaxUnitsPerCta;
+      ctas = (ctas + wave - 1) / wave * wave;
     }
+    const uint64_t max_units = (dd.units_total + ctas - 1) / ctas;
+    const uint64_t max_heads = max_units / (a.state.dim / rows_per_pass) + 2;
+    const dim3 grid(static_cast<unsigned>(ctas)), block(kUpdateThreads);
+    const size_t smem = sizeof(float) * (2 * max_units * rows_per_pass + 2 * max_heads);
+    const MxUpdateDerived& d = dd;
+#define LQ_FAST_LAUNCH(MODE_)                                                                        \
+  do {                                                                                              \
+    if (d.nblk == 8) mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 8><<<grid, block, smem, st>>>(a, d); \
+    else mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 0><<<grid, block, smem, st>>>(a, d);        \
+  } while (0)
+    switch (a.rounding.mode) {
+      case LQ_ROUND_HALF_UP: LQ_FAST_LAUNCH(LQ_ROUND_HALF_UP); break;
+      case LQ_ROUND_HALF_EVEN: LQ_FAST_LAUNCH(LQ_ROUND_HALF_EVEN); break;
+      case LQ_ROUND_PHILOX_REF: LQ_FAST_LAUNCH(LQ_ROUND_PHILOX_REF); break;
+      case LQ_ROUND_SUPPLIED: LQ_FAST_LAUNCH(LQ_ROUND_SUPPLIED); break;
+      case LQ_ROUND_PHILOX_LAYERED: LQ_FAST_LAUNCH(LQ_ROUND_PHILOX_LAYERED); break;
+      default: LQ_FAST_LAUNCH(LQ_ROUND_SUPPLIED_FIXED); break;
+    }
+#undef LQ_FAST_LAUNCH
     return;
   }
   const dim3 grid(a.state.batch * (a.state.heads / d.heads_per_cta)), block(kUpdateThreads);
