@@ -14,6 +14,8 @@
 // splits are merged with the usual (max, sum, output) rule.  The CTA that arrives last at a
 // per-(batch, kv head) ticket counter merges the splits, so no second launch and no waiting.
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "lq_common.cuh"
 
@@ -553,6 +555,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   if (threadIdx.x == 0) p.counters[b * c.kv_heads + kvh] = 0;  // ready for the next launch
 }
 
+}  // namespace lq
+
+#include "lq_int4_mma.cuh"
+
+namespace lq {
+
 // ---- host side ------------------------------------------------------------------------------------
 static int validate_cache(const lq_int4_cache& c, const char* who) {
   LQ_CHECK_ARG(c.k_packed && c.v_packed && c.k_scale && c.v_scale, "%s: null cache pointer", who);
@@ -610,8 +618,42 @@ static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   return LQ_OK;
 }
 
+template <int R, int GS>
+static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
+  using L = mma::TileLayout<GS>;
+  const size_t smem = mma::kStagesM * L::kStage + L::kNewBytes;
+  const dim3 grid(p.splits, p.a.cache.kv_heads, p.a.cache.batch), block(mma::kThreadsM);
+  if (p.a.mask) {
+    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma::int4_decode_mma_kernel<R, GS, true><<<grid, block, smem, st>>>(p);
+  } else {
+    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma::int4_decode_mma_kernel<R, GS, false><<<grid, block, smem, st>>>(p);
+  }
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+// The tensor-pipe kernel covers group sizes 32 / 64 / 128 (a 16-byte chunk of a row never straddles
+// two groups); group size 16 stays on the CUDA-core kernel.  LQ_INT4_KERNEL=cuda_core forces the
+// latter (A/B measurements).
+static bool use_mma_kernel(int gs) {
+  static const bool forced_off = [] {
+    const char* e = getenv("LQ_INT4_KERNEL");
+    return e != nullptr && strcmp(e, "cuda_core") == 0;
+  }();
+  return !forced_off && (gs == 32 || gs == 64 || gs == 128);
+}
+
 template <int R>
 static int launch_decode_gs(const DecodeParams& p, cudaStream_t st) {
+  if (use_mma_kernel(p.a.cache.group_size)) {
+    switch (p.a.cache.group_size) {
+      case 32: return launch_decode_mma<R, 32>(p, st);
+      case 64: return launch_decode_mma<R, 64>(p, st);
+      default: return launch_decode_mma<R, 128>(p, st);
+    }
+  }
   switch (p.a.cache.group_size) {
     case 16: return launch_decode<R, 16>(p, st);
     case 32: return launch_decode<R, 32>(p, st);

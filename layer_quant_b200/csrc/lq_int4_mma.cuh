@@ -1,0 +1,405 @@
+// q_len = 1 GQA decode attention over the packed INT4 KV cache on the tensor pipe.
+//
+// Per kv head the step is a small GEMM pair, S = Q K^T ([R x 128] . [128 x T]) and O = P V
+// ([R x T] . [T x 128]) with R = query heads per kv head (4 for Nemotron-H).  On CUDA cores that is
+// 4 FMAs per loaded nibble plus the unpack -- about four times the instruction issue a B200 SM can
+// spend per byte at HBM speed.  Here the multiply-accumulates go to mma.sync (m16n8k16, bf16 inputs,
+// fp32 accumulation): signed nibbles are exact in bf16 and q is bf16 already, so products are exact,
+// and what is left for the CUDA cores is unpacking (about one instruction per nibble pair), the
+// scales and the softmax.
+//
+// Layout of one 16-token step of a warp:
+//   S:  M = heads (rows 0..R-1 of the 16), N = 8 tokens, K = 16 head dims.  A 16-byte chunk of a K
+//       row (32 nibbles) is one quantisation group at group size 32, so every k-step lies inside one
+//       group and each chunk gets its own accumulator; scales are applied to the accumulators in
+//       fp32.  K nibbles reach the B fragment through ldmatrix (8 token rows x 16 bytes); the k
+//       order inside a chunk is permuted, the same permutation is baked into the Q fragments.
+//   O:  M = heads, N = 8 head dims, K = 16 tokens.  A = P * v_scale of the chunk, split into
+//       bf16 hi (rows 0..7) + lo (rows 8..15) so that P keeps 16 bits of mantissa; the two halves
+//       of the fp32 accumulator are added at the end.  V nibbles reach the B fragment through
+//       ldmatrix.trans, which hands each thread the same 4 dims of two consecutive tokens.
+// Tiles of 64 tokens are staged with 16-byte cp.async copies into a 4-stage ring; the 16-byte
+// chunks of a row are XOR-swizzled by (row >> 1) & 3 so that ldmatrix reads without bank conflicts.
+#pragma once
+
+#include "lq_common.cuh"
+
+namespace lq {
+namespace mma {
+
+constexpr int kD = 128;
+constexpr int kTileTok = 64;
+constexpr int kStagesM = 4;
+constexpr int kWarpsM = 4;
+constexpr int kThreadsM = kWarpsM * 32;
+constexpr float kNegBigM = -1.0e30f;
+constexpr float kSlackM = 8.0f;
+
+__device__ __forceinline__ uint32_t s2u(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two nibbles (bits 0..3 and 16..19 of x, already XORed with 8 so that they hold n + 8) -> bf16x2 {n, n}.
+__device__ __forceinline__ uint32_t nib_pair_to_bf16x2(uint32_t x) {
+  const uint32_t v = (x & 0x000F000Fu) | 0x43004300u;  // 128 + (n + 8), exact in bf16
+  const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), __float2bfloat162_rn(136.0f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// byte offset of 16-byte chunk c of row r in a swizzled [rows][64 B] tile
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); }
+
+template <int GS>
+struct TileLayout {
+  static constexpr int kG = kD / GS;                      // scale groups per row
+  static constexpr int kCodeBytes = kTileTok * 64;         // 4096
+  static constexpr int kScaleBytes = kTileTok * kG * 4;
+  static constexpr int kKc = 0, kVc = kCodeBytes, kKs = 2 * kCodeBytes, kVs = 2 * kCodeBytes + kScaleBytes;
+  static constexpr int kStage = 2 * kCodeBytes + 2 * kScaleBytes;
+  // the row appended in this step, as a 16-row tile of its own (row 0 real, the rest masked)
+  static constexpr int kNewKc = 0, kNewVc = 16 * 64, kNewKs = 2 * 16 * 64, kNewVs = 2 * 16 * 64 + 16 * kG * 4;
+  static constexpr int kNewBytes = 2 * 16 * 64 + 2 * 16 * kG * 4;
+};
+
+
+// One CTA (4 warps) per (split, kv head, batch); warp w owns tokens [16 w, 16 w + 16) of every
+// 64-token tile.  DecodeParams, int4_scale and int4_code come from lq_int4_kv.cu.
+template <int R, int GS, bool HAS_MASK>
+__global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const DecodeParams p) {
+  using L = TileLayout<GS>;
+  constexpr int G = L::kG;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_is_last;
+  __shared__ float s_m[kWarpsM][8], s_l[kWarpsM][8];
+
+  const lq_int4_decode_args& a = p.a;
+  const lq_int4_cache& c = a.cache;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;  // mma fragment coordinates: row / column group
+  const bool fused_new = a.k_new != nullptr;
+  uint8_t* newtile = smem + kStagesM * L::kStage;
+
+  const int ntiles = (p.ctx_len + kTileTok - 1) / kTileTok;
+  const int tile_begin = split * p.tiles_per_split;
+  const int tile_end = min(ntiles, tile_begin + p.tiles_per_split);
+  const int my_tiles = max(0, tile_end - tile_begin);
+  const bool do_new = fused_new && split == p.splits - 1;
+  if (threadIdx.x == 0) s_is_last = 0;
+
+  const int64_t kp_base = b * c.kp_stride[0] + kvh * c.kp_stride[1];
+  const int64_t vp_base = b * c.vp_stride[0] + kvh * c.vp_stride[1];
+  const int64_t ks_base = b * c.ks_stride[0] + kvh * c.ks_stride[1];
+  const int64_t vs_base = b * c.vs_stride[0] + kvh * c.vs_stride[1];
+
+  // ---- staging: every thread copies its share of a tile's 16-byte chunks ---------------------------
+  auto issue_tile = [&](int it) {
+    uint8_t* stage = smem + (it % kStagesM) * L::kStage;
+    const int tok0 = (tile_begin + it) * kTileTok;
+    const int rows = min(kTileTok, p.ctx_len - tok0);
+    const uint8_t* ksrc = c.k_packed + kp_base + static_cast<int64_t>(tok0) * 64;
+    const uint8_t* vsrc = c.v_packed + vp_base + static_cast<int64_t>(tok0) * 64;
+    for (int i = threadIdx.x; i < 2 * kTileTok * 4; i += kThreadsM) {
+      const int which = i >> 8, r = (i >> 2) & 63, ch = i & 3;
+      const bool ok = r < rows;
+      const uint8_t* src = (which ? vsrc : ksrc) + (ok ? r * 64 + ch * 16 : 0);
+      cp_async16(s2u(stage + (which ? L::kVc : L::kKc) + swz(r, ch)), src, ok ? 16u : 0u);
+    }
+    const int scale_bytes = rows * G * 4;
+    const uint8_t* kss = reinterpret_cast<const uint8_t*>(c.k_scale + ks_base + static_cast<int64_t>(tok0) * G);
+    const uint8_t* vss = reinterpret_cast<const uint8_t*>(c.v_scale + vs_base + static_cast<int64_t>(tok0) * G);
+    for (int i = threadIdx.x; i < 2 * (L::kScaleBytes / 16); i += kThreadsM) {
+      const int which = i >= L::kScaleBytes / 16;
+      const int off = (which ? i - L::kScaleBytes / 16 : i) * 16;
+      const int left = scale_bytes - off;
+      const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? static_cast<uint32_t>(left) : 0u);
+      cp_async16(s2u(stage + (which ? L::kVs : L::kKs) + off), (which ? vss : kss) + (nbytes ? off : 0), nbytes);
+    }
+  };
+
+  // ---- fused append: quantise the new K / V row, write it to the cache and into a 16-row tile -------
+  if (do_new) {
+    for (int i = threadIdx.x; i < L::kNewBytes / 16; i += kThreadsM) reinterpret_cast<uint4*>(newtile)[i] = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  if (do_new && warp < 2) {
+    const void* src = warp == 0 ? a.k_new : a.v_new;
+    const int64_t* ss = warp == 0 ? a.k_new_stride : a.v_new_stride;
+    float x[4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[i] = load_as_float(src, b * ss[0] + kvh * ss[1] + (lane * 4 + i) * ss[2], a.dtype);
+      amax = fmaxf(amax, fabsf(x[i]));
+    }
+#pragma unroll
+    for (int o = GS / 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float scale = int4_scale(amax);
+    uint32_t half = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) half |= int4_code(x[i], scale) << (4 * i);
+    const int pos = a.seq_len - 1;
+    uint8_t* gcodes = (warp == 0 ? c.k_packed + kp_base + static_cast<int64_t>(pos) * c.kp_stride[2]
+                                 : c.v_packed + vp_base + static_cast<int64_t>(pos) * c.vp_stride[2]);
+    reinterpret_cast<uint16_t*>(gcodes)[lane] = static_cast<uint16_t>(half);
+    reinterpret_cast<uint16_t*>(newtile + (warp == 0 ? L::kNewKc : L::kNewVc))[lane] = static_cast<uint16_t>(half);  // row 0: no swizzle
+    if ((lane * 4) % GS == 0) {
+      float* gsc = (warp == 0 ? c.k_scale + ks_base + static_cast<int64_t>(pos) * c.ks_stride[2]
+                              : c.v_scale + vs_base + static_cast<int64_t>(pos) * c.vs_stride[2]);
+      gsc[lane * 4 / GS] = scale;
+      reinterpret_cast<float*>(newtile + (warp == 0 ? L::kNewKs : L::kNewVs))[lane * 4 / GS] = scale;
+    }
+  }
+
+  // ---- Q fragments (A operand of S), in the k order the K unpack produces ------------------------------
+  // chunk i, k-step s (0: nibbles 0,4,1,5; 1: nibbles 2,6,3,7 of this thread's 8-nibble word)
+  uint32_t qa[4][2][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int d0 = 32 * i + 8 * t + 2 * s;
+      float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+      if (g < R) {
+        const int64_t qb = b * a.q_stride[0] + (kvh * R + g) * a.q_stride[1];
+        q0 = load_as_float(a.q, qb + (d0 + 0) * a.q_stride[2], a.dtype);
+        q1 = load_as_float(a.q, qb + (d0 + 4) * a.q_stride[2], a.dtype);
+        q2 = load_as_float(a.q, qb + (d0 + 1) * a.q_stride[2], a.dtype);
+        q3 = load_as_float(a.q, qb + (d0 + 5) * a.q_stride[2], a.dtype);
+      }
+      qa[i][s][0] = pack_bf16x2(q0, q1);  // a0: row g, k = 2t, 2t+1
+      qa[i][s][1] = pack_bf16x2(q2, q3);  // a2: row g, k = 2t+8, 2t+9
+    }
+  }
+  const float scale_sm = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
+
+  float oacc[4][4][4];  // [chunk][dim-in-chunk group s][c0, c1 (row g: hi) , c2, c3 (row g+8: lo)]
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oacc[i][s][e] = 0.0f;
+  float m_run = kNegBigM, l_run = 0.0f;  // head g of this warp's token stream (l: this lane's share)
+
+  // One 16-token step of this warp from a (swizzled) tile: rows row0 .. row0 + 15, of which the first
+  // `valid` hold tokens tok_first, tok_first + 1, ...
+  auto step16 = [&](const uint8_t* kc, const uint8_t* vc, const float* ksc, const float* vsc, int row0, int valid, int tok_first) {
+    // S = Q K^T, one accumulator per 16-byte chunk
+    float sacc[2][4][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t kr[4];
+      const uint32_t r = row0 + 8 * j + (lane & 7);
+      ldmatrix_x4(kr, s2u(kc) + swz(r, lane >> 3));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[j][i][e] = 0.0f;
+        const uint32_t w = kr[i] ^ 0x88888888u;
+        mma_bf16(sacc[j][i], qa[i][0][0], 0u, qa[i][0][1], 0u, nib_pair_to_bf16x2(w), nib_pair_to_bf16x2(w >> 4));
+        mma_bf16(sacc[j][i], qa[i][1][0], 0u, qa[i][1][1], 0u, nib_pair_to_bf16x2(w >> 8), nib_pair_to_bf16x2(w >> 12));
+      }
+    }
+    // scores of head g for tokens row0 + 8 j + 2 t + e
+    float sv[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int rr = 8 * j + 2 * t + e;
+        const float* sc = ksc + (row0 + rr) * G;
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], sacc[j][i][e], sum);
+        sum *= scale_sm;
+        if (HAS_MASK) {
+          const int n = tok_first + rr;
+          sum += (rr < valid && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
+        }
+        sv[j][e] = (rr < valid && g < R) ? sum : -INFINITY;
+      }
+    }
+    // online softmax; the running max of a head is shared by its four lanes
+    const float smax = fmaxf(fmaxf(sv[0][0], sv[0][1]), fmaxf(sv[1][0], sv[1][1]));
+    if (__any_sync(0xFFFFFFFFu, smax > m_run + kSlackM)) {
+      float rm = fmaxf(smax, __shfl_xor_sync(0xFFFFFFFFu, smax, 1));
+      rm = fmaxf(rm, __shfl_xor_sync(0xFFFFFFFFu, rm, 2));
+      const float m_new = fmaxf(m_run, rm);
+      const float alpha = exp2f(m_run - m_new);
+      l_run *= alpha;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) oacc[i][s][e] *= alpha;
+      m_run = m_new;
+    }
+    float pv[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pv[j][e] = exp2f(sv[j][e] - m_run);  // 0 for masked / padded tokens and unused rows
+        l_run += pv[j][e];
+      }
+    // O += (P * v_scale) V, chunk by chunk
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      uint32_t vr[4];
+      {
+        const int mtx = lane >> 3;
+        const uint32_t r = row0 + 8 * (mtx & 1) + (lane & 7);
+        ldmatrix_x4_trans(vr, s2u(vc) + swz(r, 2 * cp + (mtx >> 1)));
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = 2 * cp + h;
+        float pw[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float vs = vsc[(row0 + 8 * j + 2 * t + e) * G + (32 * i) / GS];
+            pw[j][e] = pv[j][e] > 0.0f ? pv[j][e] * vs : 0.0f;
+          }
+        const uint32_t a0 = pack_bf16x2(pw[0][0], pw[0][1]);
+        const uint32_t a2 = pack_bf16x2(pw[1][0], pw[1][1]);
+        const uint32_t a1 = pack_bf16x2(pw[0][0] - __uint_as_float(a0 << 16), pw[0][1] - __uint_as_float(a0 & 0xFFFF0000u));
+        const uint32_t a3 = pack_bf16x2(pw[1][0] - __uint_as_float(a2 << 16), pw[1][1] - __uint_as_float(a2 & 0xFFFF0000u));
+        const uint32_t w0 = vr[2 * h] ^ 0x88888888u, w1 = vr[2 * h + 1] ^ 0x88888888u;
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          mma_bf16(oacc[i][s], a0, a1, a2, a3, nib_pair_to_bf16x2(w0 >> (4 * s)), nib_pair_to_bf16x2(w1 >> (4 * s)));
+      }
+    }
+  };
+
+  // ---- main loop: 4-stage cp.async ring ------------------------------------------------------------------
+  for (int it = 0; it < kStagesM - 1; ++it) {
+    if (it < my_tiles) issue_tile(it);
+    cp_async_commit();
+  }
+  for (int it = 0; it < my_tiles; ++it) {
+    cp_async_wait<kStagesM - 2>();
+    __syncthreads();  // tile `it` has landed for everyone; everyone is done with tile it - 1
+    if (it + kStagesM - 1 < my_tiles) issue_tile(it + kStagesM - 1);
+    cp_async_commit();
+    const uint8_t* stage = smem + (it % kStagesM) * L::kStage;
+    const int tok0 = (tile_begin + it) * kTileTok;
+    const int rows = min(kTileTok, p.ctx_len - tok0);
+    const int row0 = 16 * warp;
+    if (row0 < rows)
+      step16(stage + L::kKc, stage + L::kVc, reinterpret_cast<const float*>(stage + L::kKs),
+             reinterpret_cast<const float*>(stage + L::kVs), row0, min(16, rows - row0), tok0 + row0);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  if (do_new && warp == 0)
+    step16(newtile + L::kNewKc, newtile + L::kNewVc, reinterpret_cast<const float*>(newtile + L::kNewKs),
+           reinterpret_cast<const float*>(newtile + L::kNewVs), 0, 1, a.seq_len - 1);
+
+  // ---- merge the warps -------------------------------------------------------------------------------------
+  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
+  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 2);
+  float* s_acc = reinterpret_cast<float*>(smem);  // [warps][R][128], reuses the ring
+  if (g < R) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        float* dst = s_acc + (warp * R + g) * kD + 32 * i + 8 * t + s;  // column 2t -> dim 32 i + 4 (2t) + s
+        dst[0] = oacc[i][s][0] + oacc[i][s][2];
+        dst[4] = oacc[i][s][1] + oacc[i][s][3];
+      }
+    if (t == 0) {
+      s_m[warp][g] = m_run;
+      s_l[warp][g] = l_run;
+    }
+  }
+  __syncthreads();
+  const int hq0 = kvh * R;
+  for (int o = threadIdx.x; o < R * kD; o += kThreadsM) {
+    const int r = o / kD, d = o - r * kD;
+    float M = kNegBigM;
+#pragma unroll
+    for (int w = 0; w < kWarpsM; ++w) M = fmaxf(M, s_m[w][r]);
+    float Lsum = 0.0f, O = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarpsM; ++w) {
+      const float fct = exp2f(s_m[w][r] - M);
+      Lsum = fmaf(s_l[w][r], fct, Lsum);
+      O = fmaf(s_acc[(w * R + r) * kD + d], fct, O);
+    }
+    if (p.splits == 1) {
+      store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / Lsum);
+    } else {
+      const int64_t slot = (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits + split;
+      p.part_acc[slot * kD + d] = O;
+      if (d == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = Lsum;
+      }
+    }
+  }
+  if (p.splits == 1) return;
+
+  // Ticket: the CTA that completes the set merges the splits.  No CTA waits for another.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&p.counters[b * c.kv_heads + kvh], 1);
+    s_is_last = (ticket == p.splits - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+  for (int o = threadIdx.x; o < R * kD; o += kThreadsM) {
+    const int r = o / kD, d = o - r * kD;
+    const int64_t slot0 = (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits;
+    float M = kNegBigM;
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slot0 + s) * 2));
+    float Lsum = 0.0f, O = 0.0f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float fct = exp2f(__ldcg(p.part_ml + (slot0 + s) * 2) - M);
+      Lsum = fmaf(__ldcg(p.part_ml + (slot0 + s) * 2 + 1), fct, Lsum);
+      O = fmaf(__ldcg(p.part_acc + (slot0 + s) * kD + d), fct, O);
+    }
+    store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / Lsum);
+  }
+  if (threadIdx.x == 0) p.counters[b * c.kv_heads + kvh] = 0;  // ready for the next launch
+}
+
+}  // namespace mma
+}  // namespace lq
