@@ -582,7 +582,7 @@ constexpr size_t kTicketBytes = kMaxTickets * sizeof(int32_t);
 
 static int pick_splits(int batch, int kv_heads, int ctx_len) {
   const int ntiles = std::max(1, (ctx_len + kTile - 1) / kTile);
-  const int sms = sm_count();
+  const int sms = 2 * sm_count();  // resident CTAs of the decode kernel: two per SM
   const int64_t base = static_cast<int64_t>(batch) * kv_heads;
   int best = 1;
   double best_score = -1.0;
@@ -593,7 +593,7 @@ static int pick_splits(int batch, int kv_heads, int ctx_len) {
     const int64_t ctas = base * s;
     const int64_t waves = (ctas + sms - 1) / sms;
     double score = static_cast<double>(ctas) / static_cast<double>(waves * sms);  // how full the last wave is
-    score *= static_cast<double>(tps) / (tps + 2.0);  // a CTA pays ~2 tiles of ramp-up and merge
+    score *= static_cast<double>(tps) / (tps + 4.0);  // a CTA pays ~4 tiles' worth of ramp-up and merge
     if (score > best_score * 1.02) {  // more splits only when they clearly pay: each adds merge traffic
       best_score = score;
       best = s;
@@ -623,13 +623,19 @@ static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
   using L = mma::TileLayout<GS>;
   const size_t smem = mma::kStagesM * L::kStage + L::kNewBytes;
   const dim3 grid(p.splits, p.a.cache.kv_heads, p.a.cache.batch), block(mma::kThreadsM);
+#define LQ_MMA_LAUNCH(MASK_, SPLIT_)                                                                                \
+  do {                                                                                                              \
+    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_>,                           \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                    \
+    mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_><<<grid, block, smem, st>>>(p);                                \
+  } while (0)
+  const bool qsplit = p.a.dtype != LQ_BF16;
   if (p.a.mask) {
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mma::int4_decode_mma_kernel<R, GS, true><<<grid, block, smem, st>>>(p);
+    if (qsplit) LQ_MMA_LAUNCH(true, true); else LQ_MMA_LAUNCH(true, false);
   } else {
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mma::int4_decode_mma_kernel<R, GS, false><<<grid, block, smem, st>>>(p);
+    if (qsplit) LQ_MMA_LAUNCH(false, true); else LQ_MMA_LAUNCH(false, false);
   }
+#undef LQ_MMA_LAUNCH
   LQ_CHECK_CUDA(cudaGetLastError());
   return LQ_OK;
 }

@@ -22,6 +22,8 @@
 // chunks of a row are XOR-swizzled by (row >> 1) & 3 so that ldmatrix reads without bank conflicts.
 #pragma once
 
+#include <type_traits>
+
 #include "lq_common.cuh"
 
 namespace lq {
@@ -64,9 +66,23 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Two nibbles (bits 0..3 and 16..19 of x, already XORed with 8 so that they hold n + 8) -> bf16x2 {n, n}.
+// 2^x by the special-function unit alone (denormal results flush to zero, which is what a softmax wants)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Two nibbles (bits 0..3 and 16..19 of x, already XORed with 8 so that they hold n + 8) -> bf16x2
+// {136 + n, 136 + n}: (x & 0x000F000F) | 0x43004300 in one LOP3 (both constants in registers).
+__device__ __forceinline__ uint32_t nib_pair_biased(uint32_t x) {
+  uint32_t v;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(x), "r"(0x000F000Fu), "r"(0x43004300u));
+  return v;
+}
+// ... -> bf16x2 {n, n}, exact
 __device__ __forceinline__ uint32_t nib_pair_to_bf16x2(uint32_t x) {
-  const uint32_t v = (x & 0x000F000Fu) | 0x43004300u;  // 128 + (n + 8), exact in bf16
+  const uint32_t v = nib_pair_biased(x);
   const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), __float2bfloat162_rn(136.0f));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
@@ -78,6 +94,21 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // byte offset of 16-byte chunk c of row r in a swizzled [rows][64 B] tile
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); }
+
+// G consecutive fp32 scales of one token from shared memory (one vector load)
+template <int G>
+__device__ __forceinline__ void load_scales(const uint8_t* p, float (&sc)[G]) {
+  if constexpr (G == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    sc[0] = v.x; sc[1] = v.y; sc[2] = v.z; sc[3] = v.w;
+  } else if constexpr (G == 2) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    sc[0] = v.x; sc[1] = v.y;
+  } else {
+    static_assert(G == 1, "group sizes 32, 64 and 128 only");
+    sc[0] = *reinterpret_cast<const float*>(p);
+  }
+}
 
 template <int GS>
 struct TileLayout {
@@ -94,8 +125,10 @@ struct TileLayout {
 
 // One CTA (4 warps) per (split, kv head, batch); warp w owns tokens [16 w, 16 w + 16) of every
 // 64-token tile.  DecodeParams, int4_scale and int4_code come from lq_int4_kv.cu.
-template <int R, int GS, bool HAS_MASK>
-__global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const DecodeParams p) {
+// QSPLIT: the query is not bf16 (fp16 / fp32 callers): it enters the tensor pipe as bf16 hi (rows 0..7)
+// + bf16 lo (rows 8..15, otherwise idle), 16 bits of mantissa in all.
+template <int R, int GS, bool HAS_MASK, bool QSPLIT>
+__global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const DecodeParams p) {
   using L = TileLayout<GS>;
   constexpr int G = L::kG;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -122,28 +155,35 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
   const int64_t ks_base = b * c.ks_stride[0] + kvh * c.ks_stride[1];
   const int64_t vs_base = b * c.vs_stride[0] + kvh * c.vs_stride[1];
 
-  // ---- staging: every thread copies its share of a tile's 16-byte chunks ---------------------------
+  // ---- staging: every thread copies the same four code chunks and (at most) one scale chunk of every tile:
+  // rows r0 and r0 + 32, chunk ch, of K and of V (the swizzle of rows r and r + 32 is the same) ---------
+  const uint32_t r0 = threadIdx.x >> 2, ch = threadIdx.x & 3;
+  const uint32_t code_src_off = r0 * 64 + ch * 16;
+  const uint32_t code_dst_off = swz(r0, ch);
+  constexpr int kScaleChunks = L::kScaleBytes / 16;          // per tensor
+  const bool has_scale_chunk = threadIdx.x < 2 * kScaleChunks;
+  const int scale_which = threadIdx.x >= kScaleChunks;       // 0: K scales, 1: V scales
+  const int scale_off = (scale_which ? threadIdx.x - kScaleChunks : threadIdx.x) * 16;
+  const uint8_t* const k_rows = c.k_packed + kp_base;
+  const uint8_t* const v_rows = c.v_packed + vp_base;
+  const uint8_t* const scale_rows = reinterpret_cast<const uint8_t*>(scale_which ? c.v_scale + vs_base : c.k_scale + ks_base);
+  const uint32_t smem_base = s2u(smem);
   auto issue_tile = [&](int it) {
-    uint8_t* stage = smem + (it % kStagesM) * L::kStage;
+    const uint32_t stage = smem_base + (it % kStagesM) * L::kStage;
     const int tok0 = (tile_begin + it) * kTileTok;
     const int rows = min(kTileTok, p.ctx_len - tok0);
-    const uint8_t* ksrc = c.k_packed + kp_base + static_cast<int64_t>(tok0) * 64;
-    const uint8_t* vsrc = c.v_packed + vp_base + static_cast<int64_t>(tok0) * 64;
-    for (int i = threadIdx.x; i < 2 * kTileTok * 4; i += kThreadsM) {
-      const int which = i >> 8, r = (i >> 2) & 63, ch = i & 3;
-      const bool ok = r < rows;
-      const uint8_t* src = (which ? vsrc : ksrc) + (ok ? r * 64 + ch * 16 : 0);
-      cp_async16(s2u(stage + (which ? L::kVc : L::kKc) + swz(r, ch)), src, ok ? 16u : 0u);
-    }
-    const int scale_bytes = rows * G * 4;
-    const uint8_t* kss = reinterpret_cast<const uint8_t*>(c.k_scale + ks_base + static_cast<int64_t>(tok0) * G);
-    const uint8_t* vss = reinterpret_cast<const uint8_t*>(c.v_scale + vs_base + static_cast<int64_t>(tok0) * G);
-    for (int i = threadIdx.x; i < 2 * (L::kScaleBytes / 16); i += kThreadsM) {
-      const int which = i >= L::kScaleBytes / 16;
-      const int off = (which ? i - L::kScaleBytes / 16 : i) * 16;
-      const int left = scale_bytes - off;
+    const int64_t tile_off = static_cast<int64_t>(tok0) * 64;
+    const uint32_t ok0 = static_cast<int>(r0) < rows ? 16u : 0u, ok1 = static_cast<int>(r0) + 32 < rows ? 16u : 0u;
+    const int64_t o0 = tile_off + (ok0 ? code_src_off : 0), o1 = tile_off + (ok1 ? code_src_off + 2048 : 0);
+    cp_async16(stage + L::kKc + code_dst_off, k_rows + o0, ok0);
+    cp_async16(stage + L::kKc + code_dst_off + 2048, k_rows + o1, ok1);
+    cp_async16(stage + L::kVc + code_dst_off, v_rows + o0, ok0);
+    cp_async16(stage + L::kVc + code_dst_off + 2048, v_rows + o1, ok1);
+    if (has_scale_chunk) {
+      const int left = rows * G * 4 - scale_off;
       const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? static_cast<uint32_t>(left) : 0u);
-      cp_async16(s2u(stage + (which ? L::kVs : L::kKs) + off), (which ? vss : kss) + (nbytes ? off : 0), nbytes);
+      cp_async16(stage + (scale_which ? L::kVs : L::kKs) + scale_off,
+                 scale_rows + static_cast<int64_t>(tok0) * (G * 4) + (nbytes ? scale_off : 0), nbytes);
     }
   };
 
@@ -183,9 +223,17 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
 
   // ---- Q fragments (A operand of S), in the k order the K unpack produces ------------------------------
   // chunk i, k-step s (0: nibbles 0,4,1,5; 1: nibbles 2,6,3,7 of this thread's 8-nibble word)
+  // The K side feeds 136 + n to the tensor pipe and starts each chunk's accumulator at -136 * sum(q over
+  // the chunk) instead (two mma per accumulator, so no long cancellation); qoff[i] is that start value
+  // for head g, the sum taken over the bf16 values the fragments actually hold.
   uint32_t qa[4][2][2];
+  uint32_t ql[QSPLIT ? 4 : 1][2][2];  // lo halves (QSPLIT only)
+  float qoff[4], qoff_lo[QSPLIT ? 4 : 1];
+  auto bf_lo = [](uint32_t v) { return __uint_as_float(v << 16); };
+  auto bf_hi = [](uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); };
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
+    float qs = 0.0f, qs_lo = 0.0f;
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       const int d0 = 32 * i + 8 * t + 2 * s;
@@ -197,8 +245,24 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
         q2 = load_as_float(a.q, qb + (d0 + 1) * a.q_stride[2], a.dtype);
         q3 = load_as_float(a.q, qb + (d0 + 5) * a.q_stride[2], a.dtype);
       }
-      qa[i][s][0] = pack_bf16x2(q0, q1);  // a0: row g, k = 2t, 2t+1
-      qa[i][s][1] = pack_bf16x2(q2, q3);  // a2: row g, k = 2t+8, 2t+9
+      const uint32_t pa = pack_bf16x2(q0, q1), pb = pack_bf16x2(q2, q3);
+      qa[i][s][0] = pa;  // a0: row g, k = 2t, 2t+1
+      qa[i][s][1] = pb;  // a2: row g, k = 2t+8, 2t+9
+      qs += (bf_lo(pa) + bf_hi(pa)) + (bf_lo(pb) + bf_hi(pb));  // of the values the fragments hold
+      if (QSPLIT) {
+        const uint32_t la = pack_bf16x2(q0 - bf_lo(pa), q1 - bf_hi(pa)), lb = pack_bf16x2(q2 - bf_lo(pb), q3 - bf_hi(pb));
+        ql[i][s][0] = la;  // a1: row g + 8
+        ql[i][s][1] = lb;  // a3
+        qs_lo += (bf_lo(la) + bf_hi(la)) + (bf_lo(lb) + bf_hi(lb));
+      }
+    }
+    qs += __shfl_xor_sync(0xFFFFFFFFu, qs, 1);  // the chunk's 32 dims live in the four lanes of row g
+    qs += __shfl_xor_sync(0xFFFFFFFFu, qs, 2);
+    qoff[i] = -136.0f * qs;
+    if (QSPLIT) {
+      qs_lo += __shfl_xor_sync(0xFFFFFFFFu, qs_lo, 1);
+      qs_lo += __shfl_xor_sync(0xFFFFFFFFu, qs_lo, 2);
+      qoff_lo[i] = -136.0f * qs_lo;
     }
   }
   const float scale_sm = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
@@ -212,51 +276,74 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
       for (int e = 0; e < 4; ++e) oacc[i][s][e] = 0.0f;
   float m_run = kNegBigM, l_run = 0.0f;  // head g of this warp's token stream (l: this lane's share)
 
-  // One 16-token step of this warp from a (swizzled) tile: rows row0 .. row0 + 15, of which the first
-  // `valid` hold tokens tok_first, tok_first + 1, ...
-  auto step16 = [&](const uint8_t* kc, const uint8_t* vc, const float* ksc, const float* vsc, int row0, int valid, int tok_first) {
+  // Per-thread offsets inside a tile for this warp's 16 rows (row0 = 16 * warp; 0 for the new-row tile):
+  // ldmatrix row addresses for K (two 8-token halves) and V (two chunk pairs), and the scale rows of
+  // the four tokens this thread owns in the S fragments (rows 8 j + 2 t + e).
+  auto make_offsets = [&](int row0, uint32_t (&koff)[2], uint32_t (&voff)[2], uint32_t (&soff)[2][2]) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) koff[j] = swz(row0 + 8 * j + (lane & 7), lane >> 3);
+    const int mtx = lane >> 3;
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) voff[cp] = swz(row0 + 8 * (mtx & 1) + (lane & 7), 2 * cp + (mtx >> 1));
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) soff[j][e] = (row0 + 8 * j + 2 * t + e) * G * 4;
+  };
+  uint32_t koff[2], voff[2], soff[2][2];
+  make_offsets(16 * warp, koff, voff, soff);
+
+  // One 16-token step of this warp.  kc / vc / ksc / vsc: shared-memory addresses of the tile's parts.
+  // FULL: all 16 rows hold tokens (no validity selects); otherwise the first `valid` rows do, and the
+  // rest were zero-filled by the staging copies (codes 0, scales 0), so they only need masking in S.
+  auto step16 = [&](auto full_tag, uint32_t kc, uint32_t vc, const uint8_t* ksc, const uint8_t* vsc, const uint32_t (&ko)[2],
+                    const uint32_t (&vo)[2], const uint32_t (&so)[2][2], int valid, int tok_first) {
+    constexpr bool FULL = decltype(full_tag)::value;
     // S = Q K^T, one accumulator per 16-byte chunk
     float sacc[2][4][4];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       uint32_t kr[4];
-      const uint32_t r = row0 + 8 * j + (lane & 7);
-      ldmatrix_x4(kr, s2u(kc) + swz(r, lane >> 3));
+      ldmatrix_x4(kr, kc + ko[j]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[j][i][e] = 0.0f;
+        sacc[j][i][0] = sacc[j][i][1] = qoff[i];
+        sacc[j][i][2] = sacc[j][i][3] = QSPLIT ? qoff_lo[QSPLIT ? i : 0] : 0.0f;
         const uint32_t w = kr[i] ^ 0x88888888u;
-        mma_bf16(sacc[j][i], qa[i][0][0], 0u, qa[i][0][1], 0u, nib_pair_to_bf16x2(w), nib_pair_to_bf16x2(w >> 4));
-        mma_bf16(sacc[j][i], qa[i][1][0], 0u, qa[i][1][1], 0u, nib_pair_to_bf16x2(w >> 8), nib_pair_to_bf16x2(w >> 12));
+        mma_bf16(sacc[j][i], qa[i][0][0], QSPLIT ? ql[QSPLIT ? i : 0][0][0] : 0u, qa[i][0][1], QSPLIT ? ql[QSPLIT ? i : 0][0][1] : 0u,
+                 nib_pair_biased(w), nib_pair_biased(w >> 4));
+        mma_bf16(sacc[j][i], qa[i][1][0], QSPLIT ? ql[QSPLIT ? i : 0][1][0] : 0u, qa[i][1][1], QSPLIT ? ql[QSPLIT ? i : 0][1][1] : 0u,
+                 nib_pair_biased(w >> 8), nib_pair_biased(w >> 12));
       }
     }
-    // scores of head g for tokens row0 + 8 j + 2 t + e
+    // scores of head g for tokens 8 j + 2 t + e of the step
     float sv[2][2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int rr = 8 * j + 2 * t + e;
-        const float* sc = ksc + (row0 + rr) * G;
+        float sc[G];
+        load_scales(ksc + so[j][e], sc);
         float sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], sacc[j][i][e], sum);
+        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], QSPLIT ? sacc[j][i][e] + sacc[j][i][e + 2] : sacc[j][i][e], sum);
         sum *= scale_sm;
+        const int rr = 8 * j + 2 * t + e;
         if (HAS_MASK) {
           const int n = tok_first + rr;
-          sum += (rr < valid && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
+          sum += ((FULL || rr < valid) && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
         }
-        sv[j][e] = (rr < valid && g < R) ? sum : -INFINITY;
+        sv[j][e] = (FULL || rr < valid) ? sum : -INFINITY;
       }
     }
-    // online softmax; the running max of a head is shared by its four lanes
+    // online softmax; the running max of a head is shared by its four lanes.  Rows g >= R carry zeros
+    // (their Q rows are zero): they run along harmlessly and are never read.
     const float smax = fmaxf(fmaxf(sv[0][0], sv[0][1]), fmaxf(sv[1][0], sv[1][1]));
     if (__any_sync(0xFFFFFFFFu, smax > m_run + kSlackM)) {
       float rm = fmaxf(smax, __shfl_xor_sync(0xFFFFFFFFu, smax, 1));
       rm = fmaxf(rm, __shfl_xor_sync(0xFFFFFFFFu, rm, 2));
       const float m_new = fmaxf(m_run, rm);
-      const float alpha = exp2f(m_run - m_new);
+      const float alpha = fast_exp2(m_run - m_new);
       l_run *= alpha;
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -271,18 +358,19 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        pv[j][e] = exp2f(sv[j][e] - m_run);  // 0 for masked / padded tokens and unused rows
+        pv[j][e] = fast_exp2(sv[j][e] - m_run);  // 0 for masked / padded tokens
         l_run += pv[j][e];
       }
+    float vsv[2][2][G];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) load_scales(vsc + so[j][e], vsv[j][e]);
     // O += (P * v_scale) V, chunk by chunk
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
       uint32_t vr[4];
-      {
-        const int mtx = lane >> 3;
-        const uint32_t r = row0 + 8 * (mtx & 1) + (lane & 7);
-        ldmatrix_x4_trans(vr, s2u(vc) + swz(r, 2 * cp + (mtx >> 1)));
-      }
+      ldmatrix_x4_trans(vr, vc + vo[cp]);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int i = 2 * cp + h;
@@ -290,10 +378,7 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float vs = vsc[(row0 + 8 * j + 2 * t + e) * G + (32 * i) / GS];
-            pw[j][e] = pv[j][e] > 0.0f ? pv[j][e] * vs : 0.0f;
-          }
+          for (int e = 0; e < 2; ++e) pw[j][e] = pv[j][e] * vsv[j][e][(32 * i) / GS];
         const uint32_t a0 = pack_bf16x2(pw[0][0], pw[0][1]);
         const uint32_t a2 = pack_bf16x2(pw[1][0], pw[1][1]);
         const uint32_t a1 = pack_bf16x2(pw[0][0] - __uint_as_float(a0 << 16), pw[0][1] - __uint_as_float(a0 & 0xFFFF0000u));
@@ -320,15 +405,22 @@ __global__ void __launch_bounds__(kThreadsM, 3) int4_decode_mma_kernel(const Dec
     const int tok0 = (tile_begin + it) * kTileTok;
     const int rows = min(kTileTok, p.ctx_len - tok0);
     const int row0 = 16 * warp;
-    if (row0 < rows)
-      step16(stage + L::kKc, stage + L::kVc, reinterpret_cast<const float*>(stage + L::kKs),
-             reinterpret_cast<const float*>(stage + L::kVs), row0, min(16, rows - row0), tok0 + row0);
+    const uint32_t sb = s2u(stage);
+    if (rows - row0 >= 16)
+      step16(std::true_type{}, sb + L::kKc, sb + L::kVc, stage + L::kKs, stage + L::kVs, koff, voff, soff, 16, tok0 + row0);
+    else if (row0 < rows)
+      step16(std::false_type{}, sb + L::kKc, sb + L::kVc, stage + L::kKs, stage + L::kVs, koff, voff, soff, rows - row0,
+             tok0 + row0);
   }
   cp_async_wait<0>();
   __syncthreads();
-  if (do_new && warp == 0)
-    step16(newtile + L::kNewKc, newtile + L::kNewVc, reinterpret_cast<const float*>(newtile + L::kNewKs),
-           reinterpret_cast<const float*>(newtile + L::kNewVs), 0, 1, a.seq_len - 1);
+  if (do_new && warp == 0) {
+    uint32_t ko0[2], vo0[2], so0[2][2];
+    make_offsets(0, ko0, vo0, so0);
+    const uint32_t nb = s2u(newtile);
+    step16(std::false_type{}, nb + L::kNewKc, nb + L::kNewVc, newtile + L::kNewKs, newtile + L::kNewVs, ko0, vo0, so0, 1,
+           a.seq_len - 1);
+  }
 
   // ---- merge the warps -------------------------------------------------------------------------------------
   l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
