@@ -359,7 +359,11 @@ def main() -> int:
             "launch_mode": "24 update launches + 1 counter bump per step, replayed from a CUDA graph",
             "eager_launch": {"GBps": bytes_step * world * args.steps / eager_sec / 1e9, "ms_per_step": eager_sec / args.steps * 1e3},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "kernel": "mx_state_update_kernel<8, packed, philox>",
+                         # ncu capture at batch 64 (profiles/mx8_state_update_layered_batch64.md), scaled by batch:
+                         # 76.9 MB read + 18.8 MB written during the launch; the rest of the 75.5 MB of writes
+                         # leaves the 126 MB L2 after the kernel has ended
+                         "traffic": (76.9e6 + 18.8e6) * B / 64, "peak_source": peak_src,
+                         "kernel": f"mx_state_update_fast_kernel<8, packed, {'PHILOX_LAYERED' if args.rng == 'layered' else 'PHILOX_REF'}, 128>",
                          "algorithmic_bytes_per_launch": MX8_BYTES_PER_SEQ_LAYER * B, "us_per_launch": per_launch_s * 1e6},
             "cpu_baseline": cpu,
             "clocks": clocks.result,
