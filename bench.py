@@ -34,6 +34,9 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# stdout carries exactly one JSON line: keep NCCL's version / info banner off it
+if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 HEADS, DIM, DSTATE, GROUPS, LAYERS = 128, 64, 128, 8, 24
 MX8_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 18 * 2  # 2,359,296
@@ -124,10 +127,11 @@ def reference_arm(args, rank: int, world: int) -> int:
         "impl": "reference", "metric": "mx8_state_update_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": len(times), "warmup": 1 if args.warmup else 0, "ms_per_step": sec * 1e3 * LAYERS, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus, batch),
+        "config": workload_config(args.gpus, batch, args.rng),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "ms_per_step extrapolates the sampled layer to the 24-layer step",
+        "note": "ms_per_step extrapolates the sampled layer to the 24-layer step; the CPU arm draws the reference's own "
+                "Philox stream (one block per value) whatever --rng says",
     }
     print(json.dumps(line), flush=True)
     return 0
