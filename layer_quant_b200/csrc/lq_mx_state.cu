@@ -380,16 +380,25 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   float* sdt = sy + n_rows;   // per touched head
   float* sdA = sdt + n_heads;
 
+  // (batch, head, row) of the slab's first row, once per CTA; rows inside the slab then need only
+  // 32-bit arithmetic
+  const int p_first = static_cast<int>(R0 % P);
+  const int h_first = static_cast<int>(bh_first % H), b_first = static_cast<int>(bh_first / H);
+  auto row_coords = [&](int i, int& b, int& h, int& p) {
+    const unsigned pi = static_cast<unsigned>(p_first + i);
+    const unsigned hh = static_cast<unsigned>(h_first) + pi / static_cast<unsigned>(P);
+    p = static_cast<int>(pi % static_cast<unsigned>(P));
+    b = b_first + static_cast<int>(hh / static_cast<unsigned>(H));
+    h = static_cast<int>(hh % static_cast<unsigned>(H));
+  };
   for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
-    const uint64_t R = R0 + i;
-    const int p = static_cast<int>(R % P);
-    const uint64_t bh = R / P;
-    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+    int b, h, p;
+    row_coords(i, b, h, p);
     sx[i] = load_as_float(a.x, b * a.x_stride[0] + h * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
   }
   for (int i = threadIdx.x; i < n_heads; i += kUpdateThreads) {
-    const uint64_t bh = bh_first + i;
-    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+    const unsigned hh = static_cast<unsigned>(h_first + i);
+    const int h = static_cast<int>(hh % static_cast<unsigned>(H)), b = b_first + static_cast<int>(hh / static_cast<unsigned>(H));
     float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1], a.dt_dtype);
     if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0], a.dt_bias_dtype);
     if (a.dt_softplus) dt = softplus_ref(dt);
@@ -399,8 +408,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   // position of the first unit: head index inside the slab, unit inside the head, head inside its group
   int head_i = 0;
   int unit_in_head = static_cast<int>(u0 % units_per_head);
-  int h_cur = static_cast<int>(bh_first % H);
-  int b_cur = static_cast<int>(bh_first / H);
+  int h_cur = h_first;
+  int b_cur = b_first;
   float Bv[16], Cv[16];
   load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, h_cur / heads_per_group, n0, Bv);
   load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
@@ -486,10 +495,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   __syncthreads();
   // y = <h', C> + D x (* z), stored for the whole slab at once
   for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
-    const uint64_t R = R0 + i;
-    const int p = static_cast<int>(R % P);
-    const uint64_t bh = R / P;
-    const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+    int b, h, p;
+    row_coords(i, b, h, p);
     float y = sy[i];
     if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
     if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
