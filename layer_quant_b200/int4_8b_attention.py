@@ -283,7 +283,7 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
     if q_len == 1:
         attn = _append_decode_attention(query_states, key_states, value_states, layer_cache, required_len,
                                         self.num_key_value_groups, group_size, attention_mask=attention_mask)
-        return self.o_proj(attn.reshape(bsz, 1, self.hidden_size)), None, past_key_value
+        return self.o_proj(attn.reshape(bsz, 1, -1)), None, past_key_value
 
     _pack_kv_into_cache(layer_cache, key_states, value_states, positions, group_size)
     k_full = self._int4_kv_repeat_kv(key_states, self.num_key_value_groups)
@@ -296,7 +296,7 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
         query_states, k_full, v_full, attn_mask=causal_mask,
         dropout_p=self.attention_dropout if self.training else 0.0,
         is_causal=causal_mask is None and q_len > 1)
-    attn = attn.transpose(1, 2).reshape(bsz, q_len, self.hidden_size)
+    attn = attn.transpose(1, 2).reshape(bsz, q_len, -1)
     return self.o_proj(attn), None, past_key_value
 
 

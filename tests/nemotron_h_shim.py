@@ -1,0 +1,209 @@
+"""A small Nemotron-H-shaped hybrid model in plain torch (TEST INFRASTRUCTURE).
+
+It stands in for the HuggingFace remote-code module the reference patches (the checkpoint, its
+modeling file, ``mamba_ssm`` and ``causal_conv1d`` are not available offline): same block layout
+(``backbone.layers[i].{block_type, norm, mixer, residual_in_fp32}``), same attribute names on the
+mixers, a module-global ``selective_state_update`` and ``repeat_kv``, and a
+``HybridMambaAttentionDynamicCache`` with ``conv_states`` / ``ssm_states`` lists -- everything
+``patch_nemotron_h_attention_int4_kv``, ``patch_nemotron_h_mamba_decode_state_kernel`` and
+``register_mamba_state_kernel_caches`` reach for.  Weights are random; the Mamba2 decode step
+follows the public Mamba2 formulation (in_proj -> causal conv1d update -> selective state update
+-> gated RMSNorm -> out_proj), attention has no RoPE, the MLP is squared-ReLU.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
+    b, h, t, d = hidden_states.shape
+    if n_rep == 1:
+        return hidden_states
+    return hidden_states[:, :, None].expand(b, h, n_rep, t, d).reshape(b, h * n_rep, t, d)
+
+
+def selective_state_update(ssm_state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False):
+    """Unquantised decode step on a floating-point state [B, H, P, N] (updated in place), fp32 math:
+    the baseline the MX kernels are compared with."""
+    batch, nheads, dim, dstate = ssm_state.shape
+    dt = dt.float()
+    if dt_bias is not None:
+        dt = dt + dt_bias.float()
+    if dt_softplus:
+        dt = F.softplus(dt)
+    ratio = nheads // B.shape[1]
+    Bh = B.float().repeat_interleave(ratio, dim=1)[:, :, None, :]
+    Ch = C.float().repeat_interleave(ratio, dim=1)[:, :, None, :]
+    dA = torch.exp(A.float()[None] * dt[..., None])
+    h = ssm_state.float() * dA + Bh * dt[..., None] * x.float()[..., None]
+    ssm_state.copy_(h.to(ssm_state.dtype))
+    y = (h * Ch).sum(-1)
+    if D is not None:
+        y = y + x.float() * D.float()
+    if z is not None:
+        y = y * z.float()
+    return y.to(x.dtype)
+
+
+class HybridMambaAttentionDynamicCache:
+    def __init__(self, config, batch_size, dtype=torch.bfloat16, device=None):
+        self.conv_states, self.ssm_states = [], []
+        conv_dim = config.mamba_intermediate + 2 * config.n_groups * config.ssm_state_size
+        for kind in config.hybrid_override_pattern:
+            if kind == "M":
+                self.conv_states.append(torch.zeros(batch_size, conv_dim, config.conv_kernel, device=device, dtype=dtype))
+                self.ssm_states.append(torch.zeros(batch_size, config.mamba_num_heads, config.mamba_head_dim,
+                                                   config.ssm_state_size, device=device, dtype=dtype))
+            else:
+                self.conv_states.append(torch.zeros(batch_size, 0, device=device, dtype=dtype))
+                self.ssm_states.append(torch.zeros(batch_size, 0, device=device, dtype=dtype))
+        self.key_cache = [None] * len(config.hybrid_override_pattern)  # bf16 KV of the unpatched attention
+        self.value_cache = [None] * len(config.hybrid_override_pattern)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim, eps=1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x, gate=None):
+        x = x.float()
+        if gate is not None:
+            x = x * F.silu(gate.float())
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (x * self.weight.float()).to(self.weight.dtype)
+
+
+class Mamba2Mixer(nn.Module):
+    def __init__(self, config, layer_idx):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.num_heads, self.head_dim = config.mamba_num_heads, config.mamba_head_dim
+        self.ssm_state_size, self.n_groups = config.ssm_state_size, config.n_groups
+        self.intermediate_size = config.mamba_intermediate
+        self.conv_dim = self.intermediate_size + 2 * self.n_groups * self.ssm_state_size
+        self.conv_kernel_size = config.conv_kernel
+        self.in_proj = nn.Linear(config.hidden_size, self.intermediate_size + self.conv_dim + self.num_heads, bias=False)
+        self.conv1d = nn.Conv1d(self.conv_dim, self.conv_dim, config.conv_kernel, groups=self.conv_dim, padding=config.conv_kernel - 1)
+        self.dt_bias = nn.Parameter(torch.rand(self.num_heads) * 2.0 - 4.0)
+        self.A_log = nn.Parameter(torch.log(torch.rand(self.num_heads) * 15.0 + 1.0))
+        self.D = nn.Parameter(torch.rand(self.num_heads))
+        self.norm = RMSNorm(self.intermediate_size)
+        self.out_proj = nn.Linear(self.intermediate_size, config.hidden_size, bias=False)
+
+    def _step(self, hs, cache_params):
+        """hs [B, hidden] -> [B, hidden]; one token through conv state and SSM state."""
+        import sys
+        module = sys.modules[__name__]
+        batch = hs.shape[0]
+        gate, xbc, dt = self.in_proj(hs).split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)
+        conv_state = cache_params.conv_states[self.layer_idx]
+        conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+        conv_state[:, :, -1] = xbc
+        xbc = F.silu((conv_state.float() * self.conv1d.weight.squeeze(1).float()).sum(-1) + self.conv1d.bias.float()).to(hs.dtype)
+        x, B, C = xbc.split([self.intermediate_size, self.n_groups * self.ssm_state_size, self.n_groups * self.ssm_state_size], dim=-1)
+        A = -torch.exp(self.A_log.float())[:, None, None].expand(-1, self.head_dim, self.ssm_state_size)
+        y = module.selective_state_update(  # looked up at call time: this is the symbol the MX patch replaces
+            cache_params.ssm_states[self.layer_idx], x.view(batch, self.num_heads, self.head_dim),
+            dt[:, :, None].expand(-1, -1, self.head_dim), A, B.view(batch, self.n_groups, -1), C.view(batch, self.n_groups, -1),
+            self.D[:, None].expand(-1, self.head_dim), z=None, dt_bias=self.dt_bias[:, None].expand(-1, self.head_dim),
+            dt_softplus=True)
+        return self.out_proj(self.norm(y.reshape(batch, -1), gate))
+
+    def forward(self, hidden_states, cache_params=None, cache_position=None, attention_mask=None):
+        # prefill and decode alike: token by token (prompts in the tests are short)
+        return torch.stack([self._step(hidden_states[:, t], cache_params) for t in range(hidden_states.shape[1])], dim=1)
+
+
+class Attention(nn.Module):
+    def __init__(self, config, layer_idx):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.hidden_size = config.hidden_size
+        self.num_heads, self.num_key_value_heads, self.head_dim = config.num_attention_heads, config.num_key_value_heads, config.head_dim
+        self.num_key_value_groups = self.num_heads // self.num_key_value_heads
+        self.attention_dropout = 0.0
+        self.q_proj = nn.Linear(self.hidden_size, self.num_heads * self.head_dim, bias=False)
+        self.k_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=False)
+        self.v_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=False)
+        self.o_proj = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=False)
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, output_attentions=False,
+                use_cache=False, cache_position=None):
+        """Unquantised reference path: bf16 K/V appended to past_key_value.key_cache / value_cache."""
+        b, t, _ = hidden_states.shape
+        q = self.q_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(b, t, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(b, t, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        if past_key_value is not None:
+            pk, pv = past_key_value.key_cache[self.layer_idx], past_key_value.value_cache[self.layer_idx]
+            if pk is not None:
+                k, v = torch.cat([pk, k], dim=2), torch.cat([pv, v], dim=2)
+            past_key_value.key_cache[self.layer_idx], past_key_value.value_cache[self.layer_idx] = k, v
+        out = F.scaled_dot_product_attention(q, repeat_kv(k, self.num_key_value_groups), repeat_kv(v, self.num_key_value_groups),
+                                             is_causal=t > 1)
+        return self.o_proj(out.transpose(1, 2).reshape(b, t, -1)), None, past_key_value
+
+
+class MLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(F.relu(self.up_proj(x)) ** 2)
+
+
+class Block(nn.Module):
+    def __init__(self, config, layer_idx, kind):
+        super().__init__()
+        self.block_type = {"M": "mamba", "*": "attention", "-": "mlp"}[kind]
+        self.residual_in_fp32 = False
+        self.norm = RMSNorm(config.hidden_size)
+        self.mixer = {"M": lambda: Mamba2Mixer(config, layer_idx), "*": lambda: Attention(config, layer_idx), "-": lambda: MLP(config)}[kind]()
+
+    def forward(self, hidden_states, cache_params=None, cache_position=None, attention_mask=None):
+        residual = hidden_states
+        hidden_states = self.norm(hidden_states.to(dtype=self.norm.weight.dtype))
+        if self.block_type == "mamba":
+            hidden_states = self.mixer(hidden_states, cache_params=cache_params, cache_position=cache_position)
+        elif self.block_type == "attention":
+            hidden_states = self.mixer(hidden_states, attention_mask=attention_mask, past_key_value=cache_params,
+                                       use_cache=cache_params is not None, cache_position=cache_position)[0]
+        else:
+            hidden_states = self.mixer(hidden_states)
+        return residual + hidden_states
+
+
+class NemotronHShimForCausalLM(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.backbone = nn.Module()
+        self.backbone.embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.backbone.layers = nn.ModuleList(Block(config, i, k) for i, k in enumerate(config.hybrid_override_pattern))
+        self.backbone.norm_f = RMSNorm(config.hidden_size)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+    @property
+    def device(self):
+        return self.lm_head.weight.device
+
+    def forward(self, input_ids, cache_params=None, cache_position=None, use_cache=True, return_dict=True, attention_mask=None):
+        h = self.backbone.embeddings(input_ids)
+        for layer in self.backbone.layers:
+            h = layer(h, cache_params=cache_params, cache_position=cache_position, attention_mask=attention_mask)
+        return SimpleNamespace(logits=self.lm_head(self.backbone.norm_f(h)))
+
+
+def tiny_config(pattern="M-M*-M-*M", hidden=256):
+    return SimpleNamespace(
+        hybrid_override_pattern=pattern, hidden_size=hidden, vocab_size=512, intermediate_size=2 * hidden,
+        num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+        mamba_num_heads=8, mamba_head_dim=64, mamba_intermediate=512, ssm_state_size=128, n_groups=2, conv_kernel=4)
