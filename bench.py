@@ -12,9 +12,10 @@ the 126 MB L2, so no launch finds its state cached from the previous step).
 
   value     algorithmic GB/s over all ranks, operands resident in HBM (18 B per 16-value block,
             read + written)
-  e2e       the same metric through the public Python call (mx_state_selective_update) with the
-            step's x / dt / B / C copied from pinned host memory and y copied back, all inside
-            the timed region
+  e2e       the same metric through the public Python API with the step's x / dt / B / C copied
+            from pinned host memory and y copied back, all inside the timed region: prepared
+            launches (MxUpdatePlan) replayed from a CUDA graph, one copy each way per step
+            (`e2e.per_call` is the plain mx_state_selective_update call per layer)
   roofline  the MX8 update kernel against the measured HBM copy bandwidth
   sweep     larger shapes of the same kernels (MX8 / MX4 at batch 256, INT4-KV decode attention
             cells), each as algorithmic GB/s and fraction of the measured peak
@@ -280,26 +281,51 @@ def main() -> int:
     per_launch_s = sec / (args.steps * LAYERS)
     achieved = MX8_BYTES_PER_SEQ_LAYER * B / per_launch_s / 1e9
 
-    # ---- end to end: host buffers in, host buffer out, through the public call ------------------------
-    host_in = []
-    for cache, o in layers8:
-        host_in.append({k: torch.empty(s, dtype=torch.bfloat16).pin_memory()
-                        for k, s in (("x", (B, HEADS, DIM)), ("dt", (B, HEADS)), ("B", (B, GROUPS, DSTATE)), ("C", (B, GROUPS, DSTATE)))})
-        for k, v in host_in[-1].items():
-            v.copy_(torch.randn(v.shape).to(torch.bfloat16))
-    host_out = [torch.empty((B, HEADS, DIM), dtype=torch.bfloat16).pin_memory() for _ in layers8]
-    dev_in = [{k: torch.empty_like(v, device=dev) for k, v in h.items()} for h in host_in]
-    h2d = sum(v.numel() * v.element_size() for v in host_in[0].values()) * LAYERS
-    d2h = host_out[0].numel() * host_out[0].element_size() * LAYERS
+    # ---- end to end: host buffers in, host buffer out, through the public calls -------------------------
+    # (a) per call: mx_state_selective_update once per layer with fresh copies of its operands, the way the
+    #     reference's decode loop calls it; (b) prepared: the step's operands of all layers in ONE pinned host
+    #     buffer -> one copy in, the 24 prepared launches (MxUpdatePlan) replayed from a CUDA graph, one copy
+    #     of all outputs back.  (b) is the number a serving loop gets and is reported as `e2e`.
+    shapes = (("x", (B, HEADS, DIM)), ("dt", (B, HEADS)), ("B", (B, GROUPS, DSTATE)), ("C", (B, GROUPS, DSTATE)))
+    per_layer = sum(int(np.prod(sh)) for _, sh in shapes)
+    host_all = torch.randn(LAYERS * per_layer).to(torch.bfloat16).pin_memory()
+    dev_all = torch.empty(LAYERS * per_layer, dtype=torch.bfloat16, device=dev)
+    out_all = torch.empty((LAYERS, B, HEADS, DIM), dtype=torch.bfloat16, device=dev)
+    host_out_all = torch.empty((LAYERS, B, HEADS, DIM), dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
-        for (cache, o), hi, di, ho in zip(layers8, host_in, dev_in, host_out):
+    def views(flat, li):
+        off, d = li * per_layer, {}
+        for k, sh in shapes:
+            n = int(np.prod(sh))
+            d[k] = flat[off:off + n].view(sh)
+            off += n
+        return d
+
+    h2d = host_all.numel() * host_all.element_size()
+    d2h = host_out_all.numel() * host_out_all.element_size()
+
+    def e2e_per_call_step():
+        for li, (cache, o) in enumerate(layers8):
+            hi, di = views(host_all, li), views(dev_all, li)
             for k in hi:
                 di[k].copy_(hi[k], non_blocking=True)
             y = mk.mx_state_selective_update(cache, di["x"], di["dt"][:, :, None].expand(B, HEADS, DIM), o["A"], di["B"], di["C"],
                                              D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True, stochastic=True, seed=0,
                                              rng_stream=args.rng)
-            ho.copy_(y, non_blocking=True)
+            host_out_all[li].copy_(y, non_blocking=True)
+
+    sec_e2e_call = timed(e2e_per_call_step, args.steps, args.warmup)
+
+    e2e_layers = []
+    for li, (cache, o) in enumerate(layers8):
+        di = views(dev_all, li)
+        e2e_layers.append((cache, dict(o, x=di["x"], dt=di["dt"][:, :, None].expand(B, HEADS, DIM), B=di["B"], C=di["C"], out=out_all[li])))
+    replay = make_step(e2e_layers, args.rng)
+
+    def e2e_step():
+        dev_all.copy_(host_all, non_blocking=True)
+        replay()
+        host_out_all.copy_(out_all, non_blocking=True)
 
     sec_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e_value = bytes_step * world * args.steps / sec_e2e / 1e9
@@ -358,7 +384,12 @@ def main() -> int:
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(world, B, args.rng),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": sec_e2e / args.steps * 1e3},
+                    "ms_per_step": sec_e2e / args.steps * 1e3,
+                    "mode": "one pinned-host -> device copy of the step's x/dt/B/C for all 24 layers, 24 prepared launches "
+                            "(MxUpdatePlan) replayed from a CUDA graph, one device -> pinned-host copy of all y",
+                    "per_call": {"value": bytes_step * world * args.steps / sec_e2e_call / 1e9,
+                                 "ms_per_step": sec_e2e_call / args.steps * 1e3,
+                                 "mode": "mx_state_selective_update called per layer, 4 copies in + 1 out per call"}},
             "gpu_launches": args.steps * (LAYERS + 1),
             "launch_mode": "24 update launches + 1 counter bump per step, replayed from a CUDA graph",
             "eager_launch": {"GBps": bytes_step * world * args.steps / eager_sec / 1e9, "ms_per_step": eager_sec / args.steps * 1e3},
