@@ -178,13 +178,21 @@ typedef struct lq_int4_decode_args {
   int32_t q_heads;
   int32_t seq_len;
   const float* mask; int64_t mask_stride_b; int64_t mask_stride_k; int32_t mask_k_len;
-  int32_t splits;
+  int32_t splits;       /* 0: the library picks; otherwise used as given, capped at the tile count and at 128 */
   void* workspace; size_t workspace_bytes;
   /* Fused append (optional): when k_new != NULL the row seq_len - 1 of every (batch, kv head) is
    * quantised from k_new / v_new [B, Hkv, D] inside the attention kernel, written to the cache
    * and used for this step, i.e. lq_int4_kv_append(q_len = 1) followed by the attention.       */
   const void* k_new; int64_t k_new_stride[3];
   const void* v_new; int64_t v_new_stride[3];
+  /* Optional device counter holding the sequence length.  When set, the kernel reads the length
+   * when it RUNS, so one recorded launch (CUDA graph) serves every step of a growing context
+   * (advance it with lq_counter_add); `seq_len` above then only sizes the launch (split count):
+   * pass the current length or the longest the recording will see.  The number of splits is fixed
+   * at launch and the tiles are dealt evenly to them on the device.  A counter outside
+   * [1, capacity] is clamped and sets bit 1 of lq_device_status.  No reference counterpart: the
+   * reference reads the length on the host each step (int4_8b_attention.py:667).               */
+  const uint64_t* seq_len_counter;
 } lq_int4_decode_args;
 
 int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_stream);
@@ -226,8 +234,9 @@ int lq_abi_version(void);
  * 2 lq_mx_update_args, 3 lq_int4_cache, 4 lq_int4_decode_args; -1 otherwise. */
 int lq_abi_sizeof(int which);
 const char* lq_last_error_string(void);
-/* Reads (and clears) the device-side status word of the current device: 0, or the code a kernel
- * recorded when one of its bounded waits ran out.  Synchronises the device. */
+/* Reads (and clears) the device-side status word of the current device: 0, or a bit set: bit 0 a
+ * bounded wait of a kernel ran out, bit 1 a seq_len_counter held a length outside [1, capacity]
+ * (the kernel clamped it).  Synchronises the device. */
 int lq_device_status(int32_t* status);
 
 #ifdef __cplusplus

@@ -78,6 +78,7 @@ class Int4DecodeArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("k_new", C.c_void_p), ("k_new_stride", C.c_int64 * 3),
         ("v_new", C.c_void_p), ("v_new_stride", C.c_int64 * 3),
+        ("seq_len_counter", C.c_void_p),
     ]
 
 

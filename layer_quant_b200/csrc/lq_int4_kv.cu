@@ -194,6 +194,27 @@ struct DecodeParams {
   float* part_acc;         // [B * Hq * splits * 128]
 };
 
+// The lengths a launch works with.  Without a device counter they are the host's; with one the
+// sequence length is read when the kernel runs (a recorded launch follows a growing context) and the
+// tiles are dealt evenly to the launch's fixed number of splits.  A counter outside [1, capacity] is
+// clamped and recorded in the device status word (bit 1).
+struct RunLengths {
+  int seq_len, ctx_len, tiles_per_split;
+};
+__device__ __forceinline__ RunLengths run_lengths(const DecodeParams& p) {
+  RunLengths r{p.a.seq_len, p.ctx_len, p.tiles_per_split};
+  if (p.a.seq_len_counter != nullptr) {
+    const unsigned long long v = *p.a.seq_len_counter;
+    const unsigned long long cap = static_cast<unsigned long long>(p.a.cache.capacity);
+    if (v < 1ull || v > cap) atomicOr(&g_int4_device_status, 2);
+    r.seq_len = static_cast<int>(v < 1ull ? 1ull : (v > cap ? cap : v));
+    r.ctx_len = r.seq_len - (p.a.k_new != nullptr ? 1 : 0);
+    const int ntiles = max(1, (r.ctx_len + kTile - 1) / kTile);
+    r.tiles_per_split = (ntiles + p.splits - 1) / p.splits;
+  }
+  return r;
+}
+
 template <int GS>
 struct StageLayout {
   static constexpr int kGroups = kHeadDim / GS;
@@ -248,9 +269,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   const bool fused_new = a.k_new != nullptr;
   uint8_t* newrow = smem + kStages * L::kBytes;
 
-  const int ntiles = (p.ctx_len + kTile - 1) / kTile;
-  const int tile_begin = split * p.tiles_per_split;
-  const int tile_end = min(ntiles, tile_begin + p.tiles_per_split);
+  const RunLengths rl = run_lengths(p);
+  const int ntiles = (rl.ctx_len + kTile - 1) / kTile;
+  const int tile_begin = split * rl.tiles_per_split;
+  const int tile_end = min(ntiles, tile_begin + rl.tiles_per_split);
   const int my_tiles = max(0, tile_end - tile_begin);
   const bool do_new = fused_new && split == p.splits - 1;
 
@@ -283,7 +305,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
     uint32_t half = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) half |= int4_code(x[i], scale) << (4 * i);
-    const int pos = a.seq_len - 1;
+    const int pos = rl.seq_len - 1;
     uint8_t* gcodes = (warp == 0 ? c.k_packed : c.v_packed) +
                       (warp == 0 ? b * c.kp_stride[0] + kvh * c.kp_stride[1] + pos * c.kp_stride[2]
                                  : b * c.vp_stride[0] + kvh * c.vp_stride[1] + pos * c.vp_stride[2]);
@@ -383,7 +405,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
   auto issue_tile = [&](int it) {
     const int st = it % kStages;
     const int tok0 = (tile_begin + it) * kTile;
-    const int rows = min(kTile, p.ctx_len - tok0);
+    const int rows = min(kTile, rl.ctx_len - tok0);
     const uint32_t code_bytes = rows * (kHeadDim / 2);
     const uint32_t scale_bytes = rows * G * 4;
     const uint32_t scale_bulk = scale_bytes & ~15u;
@@ -414,7 +436,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
       consumed = it + 1;
       const uint8_t* stage = smem + st * L::kBytes;
       const int tok0 = (tile_begin + it) * kTile;
-      const int rows = min(kTile, p.ctx_len - tok0);
+      const int rows = min(kTile, rl.ctx_len - tok0);
       uint2 kc[2], vc[2];
       float ksc[2], vsc[2], bias[2];
       int tl[2];
@@ -457,7 +479,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) int4_decode_kernel(const De
       const float vsc = reinterpret_cast<const float*>(newrow + kHeadDim + 64)[(sub * 16) / GS];
       float bias = 0.0f;
       if (HAS_MASK) {
-        const int n = a.seq_len - 1;
+        const int n = rl.seq_len - 1;
         bias = n < a.mask_k_len ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
       }
       process_token(warp == 0 && tg == 0, kc, vc, ksc, vsc, bias);
@@ -582,7 +604,7 @@ constexpr size_t kTicketBytes = kMaxTickets * sizeof(int32_t);
 
 static int pick_splits(int batch, int kv_heads, int ctx_len) {
   const int ntiles = std::max(1, (ctx_len + kTile - 1) / kTile);
-  const int sms = 2 * sm_count();  // resident CTAs of the decode kernel: two per SM
+  const int sms = 3 * sm_count();  // resident CTAs of the decode kernel: three per SM (bf16 queries, up to 4 per kv head)
   const int64_t base = static_cast<int64_t>(batch) * kv_heads;
   int best = 1;
   double best_score = -1.0;
@@ -751,7 +773,7 @@ LQ_EXPORT int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_st
   p.ctx_len = a.seq_len - (a.k_new ? 1 : 0);
   const int ntiles = std::max(1, (p.ctx_len + kTile - 1) / kTile);
   int splits = a.splits > 0 ? a.splits : pick_splits(c.batch, c.kv_heads, std::max(p.ctx_len, 1));
-  splits = std::max(1, std::min(splits, ntiles));
+  splits = std::max(1, std::min(std::min(splits, ntiles), mma::kMaxSplitsM));  // the merge holds one factor per split in shared memory
   int tps = (ntiles + splits - 1) / splits;
   splits = (ntiles + tps - 1) / tps;  // no empty splits
   p.splits = splits;

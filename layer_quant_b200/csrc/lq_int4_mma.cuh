@@ -36,6 +36,7 @@ constexpr int kWarpsM = 4;
 constexpr int kThreadsM = kWarpsM * 32;
 constexpr float kNegBigM = -1.0e30f;
 constexpr float kSlackM = 8.0f;
+constexpr int kMaxSplitsM = 128;  // the merge keeps one factor per (head, split) in shared memory
 
 __device__ __forceinline__ uint32_t s2u(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -73,11 +74,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Two nibbles (bits 0..3 and 16..19 of x, already XORed with 8 so that they hold n + 8) -> bf16x2
-// {136 + n, 136 + n}: (x & 0x000F000F) | 0x43004300 in one LOP3 (both constants in registers).
+// Two two's-complement nibbles n (bits 0..3 and 16..19 of x) -> bf16x2 {136 + n, 136 + n} in one LOP3:
+// with M = 0x000F000F and K = 0x43084308 the result is (x ^ K) where M is set and K elsewhere, i.e. the
+// nibble with its top bit flipped (n + 8) under the bf16 pattern of 128.
 __device__ __forceinline__ uint32_t nib_pair_biased(uint32_t x) {
   uint32_t v;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(x), "r"(0x000F000Fu), "r"(0x43004300u));
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(x), "r"(0x000F000Fu), "r"(0x43084308u));
   return v;
 }
 // ... -> bf16x2 {n, n}, exact
@@ -93,6 +95,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // byte offset of 16-byte chunk c of row r in a swizzled [rows][64 B] tile
+// D = A B + C with C in registers of its own: an accumulator starts from values that stay where they are
+__device__ __forceinline__ void mma_bf16_from(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1, float c0, float c1, float c2, float c3) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); }
 
 // G consecutive fp32 scales of one token from shared memory (one vector load)
@@ -128,7 +139,7 @@ struct TileLayout {
 // QSPLIT: the query is not bf16 (fp16 / fp32 callers): it enters the tensor pipe as bf16 hi (rows 0..7)
 // + bf16 lo (rows 8..15, otherwise idle), 16 bits of mantissa in all.
 template <int R, int GS, bool HAS_MASK, bool QSPLIT>
-__global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_decode_mma_kernel(const DecodeParams p) {
   using L = TileLayout<GS>;
   constexpr int G = L::kG;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -140,12 +151,22 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;  // mma fragment coordinates: row / column group
+  // Rows of the S fragments.  Up to four query heads per kv head: rows 4..7 repeat rows 0..3, so that
+  // lane row g holds the scores of head g & 3 and the O^T product below can take the bf16 hi part of
+  // P * v_scale from rows 0..3 and the lo part from rows 4..7 as the eight columns of ONE n-tile.
+  // Eight heads: rows are heads, hi and lo parts go to two n-tiles.
+  constexpr bool DUP = R <= 4;
+  constexpr int NT = DUP ? 1 : 2;
+  const int hrow = DUP ? (g & 3) : g;
+  const bool is_lo = DUP && g >= 4;
+  const uint32_t lo_mul = is_lo ? 65536u : 0u, lo_mask = is_lo ? 0xFFFF0000u : 0u;
   const bool fused_new = a.k_new != nullptr;
   uint8_t* newtile = smem + kStagesM * L::kStage;
 
-  const int ntiles = (p.ctx_len + kTileTok - 1) / kTileTok;
-  const int tile_begin = split * p.tiles_per_split;
-  const int tile_end = min(ntiles, tile_begin + p.tiles_per_split);
+  const RunLengths rl = run_lengths(p);
+  const int ntiles = (rl.ctx_len + kTileTok - 1) / kTileTok;
+  const int tile_begin = split * rl.tiles_per_split;
+  const int tile_end = min(ntiles, tile_begin + rl.tiles_per_split);
   const int my_tiles = max(0, tile_end - tile_begin);
   const bool do_new = fused_new && split == p.splits - 1;
   if (threadIdx.x == 0) s_is_last = 0;
@@ -171,7 +192,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
   auto issue_tile = [&](int it) {
     const uint32_t stage = smem_base + (it % kStagesM) * L::kStage;
     const int tok0 = (tile_begin + it) * kTileTok;
-    const int rows = min(kTileTok, p.ctx_len - tok0);
+    const int rows = min(kTileTok, rl.ctx_len - tok0);
     const int64_t tile_off = static_cast<int64_t>(tok0) * 64;
     const uint32_t ok0 = static_cast<int>(r0) < rows ? 16u : 0u, ok1 = static_cast<int>(r0) + 32 < rows ? 16u : 0u;
     const int64_t o0 = tile_off + (ok0 ? code_src_off : 0), o1 = tile_off + (ok1 ? code_src_off + 2048 : 0);
@@ -208,7 +229,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
     uint32_t half = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) half |= int4_code(x[i], scale) << (4 * i);
-    const int pos = a.seq_len - 1;
+    const int pos = rl.seq_len - 1;
     uint8_t* gcodes = (warp == 0 ? c.k_packed + kp_base + static_cast<int64_t>(pos) * c.kp_stride[2]
                                  : c.v_packed + vp_base + static_cast<int64_t>(pos) * c.vp_stride[2]);
     reinterpret_cast<uint16_t*>(gcodes)[lane] = static_cast<uint16_t>(half);
@@ -238,8 +259,8 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
     for (int s = 0; s < 2; ++s) {
       const int d0 = 32 * i + 8 * t + 2 * s;
       float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-      if (g < R) {
-        const int64_t qb = b * a.q_stride[0] + (kvh * R + g) * a.q_stride[1];
+      if (hrow < R) {
+        const int64_t qb = b * a.q_stride[0] + (kvh * R + hrow) * a.q_stride[1];
         q0 = load_as_float(a.q, qb + (d0 + 0) * a.q_stride[2], a.dtype);
         q1 = load_as_float(a.q, qb + (d0 + 4) * a.q_stride[2], a.dtype);
         q2 = load_as_float(a.q, qb + (d0 + 1) * a.q_stride[2], a.dtype);
@@ -267,14 +288,19 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
   }
   const float scale_sm = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
 
-  float oacc[4][4][4];  // [chunk][dim-in-chunk group s][c0, c1 (row g: hi) , c2, c3 (row g+8: lo)]
+  // O^T accumulators: m-tile (chunk i, half sp) has row g = dim 32 i + 4 g + 2 sp and row g + 8 = that
+  // dim + 1; columns 2t, 2t+1 are heads (DUP: head c & 3, hi part for c < 4, lo part for c >= 4).
+  float oacc[4][2][NT][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int s = 0; s < 4; ++s)
+    for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) oacc[i][s][e] = 0.0f;
-  float m_run = kNegBigM, l_run = 0.0f;  // head g of this warp's token stream (l: this lane's share)
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[i][sp][nt][e] = 0.0f;
+  const int col_head0 = DUP ? ((2 * t) & 3) : 2 * t;  // head of accumulator column 2t (column 2t+1: the next head)
+  float m_run = kNegBigM, l_run = 0.0f;  // head hrow of this warp's token stream (l: this lane's share)
 
   // Per-thread offsets inside a tile for this warp's 16 rows (row0 = 16 * warp; 0 for the new-row tile):
   // ldmatrix row addresses for K (two 8-token halves) and V (two chunk pairs), and the scale rows of
@@ -299,34 +325,30 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
   auto step16 = [&](auto full_tag, uint32_t kc, uint32_t vc, const uint8_t* ksc, const uint8_t* vsc, const uint32_t (&ko)[2],
                     const uint32_t (&vo)[2], const uint32_t (&so)[2][2], int valid, int tok_first) {
     constexpr bool FULL = decltype(full_tag)::value;
-    // S = Q K^T, one accumulator per 16-byte chunk
-    float sacc[2][4][4];
+    // S = Q K^T, one accumulator per 16-byte chunk; scores of head g for tokens 8 j + 2 t + e of the step
+    float sv[2][2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
+      float sacc[4][4];
       uint32_t kr[4];
       ldmatrix_x4(kr, kc + ko[j]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        sacc[j][i][0] = sacc[j][i][1] = qoff[i];
-        sacc[j][i][2] = sacc[j][i][3] = QSPLIT ? qoff_lo[QSPLIT ? i : 0] : 0.0f;
-        const uint32_t w = kr[i] ^ 0x88888888u;
-        mma_bf16(sacc[j][i], qa[i][0][0], QSPLIT ? ql[QSPLIT ? i : 0][0][0] : 0u, qa[i][0][1], QSPLIT ? ql[QSPLIT ? i : 0][0][1] : 0u,
-                 nib_pair_biased(w), nib_pair_biased(w >> 4));
-        mma_bf16(sacc[j][i], qa[i][1][0], QSPLIT ? ql[QSPLIT ? i : 0][1][0] : 0u, qa[i][1][1], QSPLIT ? ql[QSPLIT ? i : 0][1][1] : 0u,
+        const float c_lo = QSPLIT ? qoff_lo[QSPLIT ? i : 0] : 0.0f;
+        const uint32_t w = kr[i];
+        mma_bf16_from(sacc[i], qa[i][0][0], QSPLIT ? ql[QSPLIT ? i : 0][0][0] : 0u, qa[i][0][1],
+                      QSPLIT ? ql[QSPLIT ? i : 0][0][1] : 0u, nib_pair_biased(w), nib_pair_biased(w >> 4), qoff[i], qoff[i], c_lo,
+                      c_lo);
+        mma_bf16(sacc[i], qa[i][1][0], QSPLIT ? ql[QSPLIT ? i : 0][1][0] : 0u, qa[i][1][1], QSPLIT ? ql[QSPLIT ? i : 0][1][1] : 0u,
                  nib_pair_biased(w >> 8), nib_pair_biased(w >> 12));
       }
-    }
-    // scores of head g for tokens 8 j + 2 t + e of the step
-    float sv[2][2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         float sc[G];
         load_scales(ksc + so[j][e], sc);
         float sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], QSPLIT ? sacc[j][i][e] + sacc[j][i][e + 2] : sacc[j][i][e], sum);
+        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], QSPLIT ? sacc[i][e] + sacc[i][e + 2] : sacc[i][e], sum);
         sum *= scale_sm;
         const int rr = 8 * j + 2 * t + e;
         if (HAS_MASK) {
@@ -345,12 +367,19 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
       const float m_new = fmaxf(m_run, rm);
       const float alpha = fast_exp2(m_run - m_new);
       l_run *= alpha;
+      const float alpha0 = __shfl_sync(0xFFFFFFFFu, alpha, 4 * col_head0);  // the factors of this thread's two columns
+      const float alpha1 = __shfl_sync(0xFFFFFFFFu, alpha, 4 * col_head0 + 4);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
+        for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) oacc[i][s][e] *= alpha;
+          for (int nt = 0; nt < NT; ++nt) {
+            oacc[i][sp][nt][0] *= alpha0;
+            oacc[i][sp][nt][1] *= alpha1;
+            oacc[i][sp][nt][2] *= alpha0;
+            oacc[i][sp][nt][3] *= alpha1;
+          }
       m_run = m_new;
     }
     float pv[2][2];
@@ -365,8 +394,29 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) load_scales(vsc + so[j][e], vsv[j][e]);
-    // O += (P * v_scale) V, chunk by chunk
+      for (int e = 0; e < 2; ++e) {
+        load_scales(vsc + so[j][e], vsv[j][e]);
+#pragma unroll
+        for (int q = 0; q < G; ++q) vsv[j][e][q] *= pv[j][e];  // P * v_scale per group, kept instead of P and the scales
+      }
+    // B operand of O^T: (P * v_scale)^T per scale group, k = the tokens 2t, 2t+1 (+8), n = row g.  A lane of
+    // rows 0..3 keeps the bf16 rounding of the product, a lane of rows 4..7 the bf16 rounding of what that
+    // left over (one formula: the part taken off is masked to zero on the hi lanes).
+    uint32_t pb[G][2][NT];
+#pragma unroll
+    for (int q = 0; q < G; ++q)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = vsv[j][0][q], p1 = vsv[j][1][q];
+        const uint32_t hi = pack_bf16x2(p0, p1);
+        if (DUP) {
+          pb[q][j][0] = pack_bf16x2(p0 - __uint_as_float(hi * lo_mul), p1 - __uint_as_float(hi & lo_mask));
+        } else {
+          pb[q][j][0] = hi;
+          pb[q][j][NT - 1] = pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xFFFF0000u));
+        }
+      }
+    // O^T += V^T (P * v_scale)^T, chunk by chunk: the unpacked codes are the A operand
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
       uint32_t vr[4];
@@ -374,19 +424,15 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int i = 2 * cp + h;
-        float pw[2][2];
+        const int q = (32 * i) / GS;
+        const uint32_t w0 = vr[2 * h], w1 = vr[2 * h + 1];
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int sp = 0; sp < 2; ++sp) {
+          const uint32_t a0 = nib_pair_to_bf16x2(w0 >> (8 * sp)), a1 = nib_pair_to_bf16x2(w0 >> (8 * sp + 4));
+          const uint32_t a2 = nib_pair_to_bf16x2(w1 >> (8 * sp)), a3 = nib_pair_to_bf16x2(w1 >> (8 * sp + 4));
 #pragma unroll
-          for (int e = 0; e < 2; ++e) pw[j][e] = pv[j][e] * vsv[j][e][(32 * i) / GS];
-        const uint32_t a0 = pack_bf16x2(pw[0][0], pw[0][1]);
-        const uint32_t a2 = pack_bf16x2(pw[1][0], pw[1][1]);
-        const uint32_t a1 = pack_bf16x2(pw[0][0] - __uint_as_float(a0 << 16), pw[0][1] - __uint_as_float(a0 & 0xFFFF0000u));
-        const uint32_t a3 = pack_bf16x2(pw[1][0] - __uint_as_float(a2 << 16), pw[1][1] - __uint_as_float(a2 & 0xFFFF0000u));
-        const uint32_t w0 = vr[2 * h] ^ 0x88888888u, w1 = vr[2 * h + 1] ^ 0x88888888u;
-#pragma unroll
-        for (int s = 0; s < 4; ++s)
-          mma_bf16(oacc[i][s], a0, a1, a2, a3, nib_pair_to_bf16x2(w0 >> (4 * s)), nib_pair_to_bf16x2(w1 >> (4 * s)));
+          for (int nt = 0; nt < NT; ++nt) mma_bf16(oacc[i][sp][nt], a0, a1, a2, a3, pb[q][0][nt], pb[q][1][nt]);
+        }
       }
     }
   };
@@ -403,7 +449,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
     cp_async_commit();
     const uint8_t* stage = smem + (it % kStagesM) * L::kStage;
     const int tok0 = (tile_begin + it) * kTileTok;
-    const int rows = min(kTileTok, p.ctx_len - tok0);
+    const int rows = min(kTileTok, rl.ctx_len - tok0);
     const int row0 = 16 * warp;
     const uint32_t sb = s2u(stage);
     if (rows - row0 >= 16)
@@ -419,26 +465,33 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
     make_offsets(0, ko0, vo0, so0);
     const uint32_t nb = s2u(newtile);
     step16(std::false_type{}, nb + L::kNewKc, nb + L::kNewVc, newtile + L::kNewKs, newtile + L::kNewVs, ko0, vo0, so0, 1,
-           a.seq_len - 1);
+           rl.seq_len - 1);
   }
 
   // ---- merge the warps -------------------------------------------------------------------------------------
   l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
   l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 2);
   float* s_acc = reinterpret_cast<float*>(smem);  // [warps][R][128], reuses the ring
-  if (g < R) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        float* dst = s_acc + (warp * R + g) * kD + 32 * i + 8 * t + s;  // column 2t -> dim 32 i + 4 (2t) + s
-        dst[0] = oacc[i][s][0] + oacc[i][s][2];
-        dst[4] = oacc[i][s][1] + oacc[i][s][3];
+    for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v;
+        if (DUP) {
+          v = oacc[i][sp][0][e];
+          v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);  // hi columns (t < 2) + lo columns (t >= 2) of the same heads
+        } else {
+          v = oacc[i][sp][0][e] + oacc[i][sp][NT - 1][e];
+        }
+        const int head = col_head0 + (e & 1);
+        const int dim = 32 * i + 4 * g + 2 * sp + (e >> 1);
+        if ((!DUP || t < 2) && head < R) s_acc[(warp * R + head) * kD + dim] = v;
       }
-    if (t == 0) {
-      s_m[warp][g] = m_run;
-      s_l[warp][g] = l_run;
-    }
+  if (g < R && t == 0) {
+    s_m[warp][g] = m_run;
+    s_l[warp][g] = l_run;
   }
   __syncthreads();
   const int hq0 = kvh * R;
@@ -477,18 +530,34 @@ __global__ void __launch_bounds__(kThreadsM, 2) int4_decode_mma_kernel(const Dec
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
+  // (1) one warp per head: the maximum over the splits, each split's factor (to shared memory) and the
+  // denominator; (2) one thread per output: the weighted sum, its loads independent of one another.
+  float* s_f = reinterpret_cast<float*>(smem);  // [R][kMaxSplitsM], reuses the ring
+  float* s_den = s_f + R * kMaxSplitsM;         // [R]
+  for (int r = warp; r < R; r += kWarpsM) {
+    const float* ml = p.part_ml + (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits * 2;
+    float M = kNegBigM;
+    for (int s = lane; s < p.splits; s += 32) M = fmaxf(M, __ldcg(ml + 2 * s));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    float den = 0.0f;
+    for (int s = lane; s < p.splits; s += 32) {
+      const float fct = exp2f(__ldcg(ml + 2 * s) - M);
+      s_f[r * kMaxSplitsM + s] = fct;
+      den = fmaf(__ldcg(ml + 2 * s + 1), fct, den);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, o);
+    if (lane == 0) s_den[r] = den;
+  }
+  __syncthreads();
   for (int o = threadIdx.x; o < R * kD; o += kThreadsM) {
     const int r = o / kD, d = o - r * kD;
-    const int64_t slot0 = (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits;
-    float M = kNegBigM;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slot0 + s) * 2));
-    float Lsum = 0.0f, O = 0.0f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float fct = exp2f(__ldcg(p.part_ml + (slot0 + s) * 2) - M);
-      Lsum = fmaf(__ldcg(p.part_ml + (slot0 + s) * 2 + 1), fct, Lsum);
-      O = fmaf(__ldcg(p.part_acc + (slot0 + s) * kD + d), fct, O);
-    }
-    store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / Lsum);
+    const float* acc = p.part_acc + (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits * kD + d;
+    float O = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < p.splits; ++s) O = fmaf(__ldcg(acc + static_cast<int64_t>(s) * kD), s_f[r * kMaxSplitsM + s], O);
+    store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / s_den[r]);
   }
   if (threadIdx.x == 0) p.counters[b * c.kv_heads + kvh] = 0;  // ready for the next launch
 }

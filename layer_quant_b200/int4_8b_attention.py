@@ -186,9 +186,11 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-def _launch_decode(query_states, cache, seq_len, group_size, mask, k_new=None, v_new=None, splits=0, out=None):
+def _decode_args(query_states, cache, seq_len, group_size, mask, k_new=None, v_new=None, splits=0, out=None,
+                 seq_len_counter=None):
+    """Fill the argument block of ``lq_int4_decode_attn``.  Returns (args, out, tensors the block points to)."""
     batch, n_heads, q_len, head_dim = query_states.shape
-    dev = _lib.require_cuda(query_states, mask, k_new, v_new)
+    dev = _lib.require_cuda(query_states, mask, k_new, v_new, seq_len_counter)
     if out is None:
         out = torch.empty((batch, n_heads, head_dim), device=dev, dtype=query_states.dtype)
     a = _lib.Int4DecodeArgs()
@@ -211,16 +213,58 @@ def _launch_decode(query_states, cache, seq_len, group_size, mask, k_new=None, v
         for i, ax in enumerate((0, 1, 3)):
             a.k_new_stride[i] = k_new.stride(ax)
             a.v_new_stride[i] = v_new.stride(ax)
+    if seq_len_counter is not None:
+        if seq_len_counter.dtype != torch.int64 or seq_len_counter.numel() != 1:
+            raise TypeError("seq_len_counter must be a one-element int64 CUDA tensor")
+        a.seq_len_counter = seq_len_counter.data_ptr()
     l = _lib.lib()
     if splits <= 0:
         splits = l.lq_int4_decode_auto_splits(batch, a.cache.kv_heads, max(seq_len - (1 if k_new is not None else 0), 1))
     a.splits = splits
+    ws = None
     if splits > 1:
         need = l.lq_int4_decode_workspace_bytes(batch, n_heads, a.cache.kv_heads, head_dim, splits)
         ws = _workspace(dev, need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-    _lib.check(l.lq_int4_decode_attn(ct.byref(a), _lib.stream_ptr(dev)))
+    return a, out, (query_states, cache, mask, k_new, v_new, seq_len_counter, ws, out)
+
+
+def _launch_decode(query_states, cache, seq_len, group_size, mask, k_new=None, v_new=None, splits=0, out=None):
+    a, out, _keep = _decode_args(query_states, cache, seq_len, group_size, mask, k_new, v_new, splits, out)
+    _lib.check(_lib.lib().lq_int4_decode_attn(ct.byref(a), _lib.stream_ptr(out.device)))
     return out
+
+
+class Int4DecodePlan:
+    """A decode-attention launch prepared once (not in the reference, which rebuilds its launch every
+    step, int4_8b_attention.py:518-566): the argument block is filled here and ``launch()`` is a single
+    foreign call on the current stream, reading whatever the bound tensors hold at that time.
+
+    With ``seq_len_counter`` (one-element int64 CUDA tensor) the kernel takes the sequence length from
+    the device when it runs; ``seq_len`` then only sizes the launch.  Such a plan can be recorded in a
+    CUDA graph once and replayed for every decode step: write the new token's q / k / v into the bound
+    tensors, replay, and advance the counter on the stream (``advance_seq_len``).  The caller keeps the
+    cache capacity ahead of the counter."""
+
+    def __init__(self, query_states, cache, seq_len, group_size, *, k_new=None, v_new=None, mask=None, splits=0,
+                 out=None, seq_len_counter=None):
+        if query_states.shape[2] != 1:
+            raise ValueError(f"Fused INT4 decode attention expects q_len=1, got {query_states.shape[2]}")
+        self.args, self.out, self._keep = _decode_args(query_states, cache, seq_len, group_size, mask, k_new, v_new, splits,
+                                                       out, seq_len_counter)
+        self._ref = ct.byref(self.args)
+        self._fn = _lib.lib().lq_int4_decode_attn
+        self.device = self.out.device
+        self.seq_len_counter = seq_len_counter
+
+    def launch(self) -> torch.Tensor:
+        _lib.check(self._fn(self._ref, _lib.stream_ptr(self.device)))
+        return self.out
+
+
+def advance_seq_len(seq_len_counter: torch.Tensor, inc: int = 1) -> None:
+    """``*seq_len_counter += inc`` on the current stream (a one-thread kernel; records into CUDA graphs)."""
+    _lib.check(_lib.lib().lq_counter_add(seq_len_counter.data_ptr(), int(inc), _lib.stream_ptr(seq_len_counter.device)))
 
 
 def _decode_attention(query_states: torch.Tensor, cache: Int4KVLayerCache, seq_len: int, num_key_value_groups: int,

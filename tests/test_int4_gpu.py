@@ -263,3 +263,48 @@ def test_workspace_is_reusable_across_problem_sizes():
         ref = oracle.int4_decode_attention(q[:, :, 0], *cache_np(cache), tlen, 32)
         for _ in range(2):
             assert_out_close(m._decode_attention(t(q), cache, tlen, 4, 32, splits=splits), ref)
+
+
+@pytest.mark.parametrize("gs,dtype", [(32, torch.bfloat16), (16, torch.float32)])
+def test_recorded_launch_follows_device_length(gs, dtype):
+    """One prepared launch, recorded in a CUDA graph with the sequence length in a device counter, is
+    replayed for ten decode steps; every step must equal the per-step call (same appended bytes, outputs
+    within the output tolerance: the split boundaries differ) and the float64 oracle."""
+    m = ia()
+    from layer_quant_b200 import _lib
+    b, hkv, hq, start, steps, cap = 2, 2, 8, 150, 10, 512
+    k, v = make_kv(21, b, hkv, start + steps)
+    rng = np.random.default_rng(22)
+    qs = bf16r(rng.standard_normal((steps, b, hq, 1, 128)).astype(np.float32))
+    ref_cache = fill_cache(m, k[:, :, :start], v[:, :, :start], gs, capacity=cap, dtype=dtype)
+    cache = fill_cache(m, k[:, :, :start], v[:, :, :start], gs, capacity=cap, dtype=dtype)
+    q_buf = torch.zeros((b, hq, 1, 128), device=dev(), dtype=dtype)
+    k_buf = torch.zeros((b, hkv, 1, 128), device=dev(), dtype=dtype)
+    v_buf = torch.zeros_like(k_buf)
+    counter = torch.full((1,), start + 1, device=dev(), dtype=torch.int64)
+    plan = m.Int4DecodePlan(q_buf, cache, cap, gs, k_new=k_buf, v_new=v_buf, splits=3, seq_len_counter=counter)
+    plan.launch()  # warm-up outside the recording (row `start` is rewritten by the first replay)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plan.launch()
+        m.advance_seq_len(counter)
+    for i in range(steps):
+        n = start + i + 1
+        q_buf.copy_(t(qs[i], dtype))
+        k_buf.copy_(t(k[:, :, n - 1:n], dtype))
+        v_buf.copy_(t(v[:, :, n - 1:n], dtype))
+        graph.replay()
+        want = m._append_decode_attention(q_buf, k_buf, v_buf, ref_cache, n, hq // hkv, gs)
+        ref = oracle.int4_decode_attention(qs[i][:, :, 0], *cache_np(ref_cache), n, gs)
+        assert_out_close(want, ref)
+        assert_out_close(plan.out, ref)
+    assert int(counter.item()) == start + steps + 1
+    for got, want in zip(cache_np(cache), cache_np(ref_cache)):
+        np.testing.assert_array_equal(got[:, :, :start + steps], want[:, :, :start + steps])
+    assert _lib.device_status() == 0
+    # a counter beyond the capacity is clamped and reported, not followed
+    counter.fill_(cap + 7)
+    plan.launch()
+    assert _lib.device_status() & 2
+    assert _lib.device_status() == 0  # reading clears it
