@@ -42,6 +42,7 @@ if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
 HEADS, DIM, DSTATE, GROUPS, LAYERS = 128, 64, 128, 8, 24
 MX8_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 18 * 2  # 2,359,296
 MX4_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 10 * 2  # 1,310,720
+BF16_BYTES_PER_SEQ_LAYER = HEADS * DIM * DSTATE * 2 * 2  # 4,194,304
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -344,6 +345,30 @@ def main() -> int:
                 sweep[f"mx{bits}_update_b256_{name}_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
                                                                "us_per_launch": round(s / 20 * 1e6, 1)}
             del big
+            torch.cuda.empty_cache()
+        # the other batches of the MX4 comparison (one layer each, larger than L2) and the BF16 state it is compared with
+        for bb in (64, 1024):
+            big = make_layers(bb, 1, 4)
+            s = timed(make_step(big, "layered"), 5, 3)
+            gbs = MX4_BYTES_PER_SEQ_LAYER * bb * 5 / s / 1e9
+            sweep[f"mx4_update_b{bb}_layered_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                         "us_per_launch": round(s / 5 * 1e6, 1)}
+            del big
+            torch.cuda.empty_cache()
+        from layer_quant_b200 import dense_state
+        for bb in (64, 256):
+            nlay = 4
+            states = [torch.randn(bb, 128, 64, 128, generator=gen, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(nlay)]
+            ops = make_layers(bb, 1, 8)[0][1]
+            def dense_step():
+                for st in states:
+                    dense_state.selective_state_update(st, ops["x"], ops["dt"], ops["A"], ops["B"], ops["C"], D=ops["D"],
+                                                       dt_bias=ops["dt_bias"], dt_softplus=True, out=ops["out"])
+            s = timed(dense_step, 5, 3)
+            gbs = BF16_BYTES_PER_SEQ_LAYER * bb * nlay * 5 / s / 1e9
+            sweep[f"bf16_state_update_b{bb}"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                 "us_per_launch": round(s / (5 * nlay) * 1e6, 1)}
+            del states, ops
             torch.cuda.empty_cache()
         for (bb, ctx) in ((1, 1024), (1, 131072), (8, 32768), (16, 8192), (64, 32768), (256, 8192)):
             cap = ctx

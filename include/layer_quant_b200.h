@@ -230,8 +230,54 @@ size_t lq_int4_static_scratch_bytes(void);
 /* Library                                                                                    */
 /* ------------------------------------------------------------------------------------------ */
 int lq_abi_version(void);
+/* ---- Unquantised baselines: the step before the hot path and the state format it is compared with ----
+ *
+ * The reference takes both from third-party packages that are not part of its tree: the patched
+ * global `selective_state_update` it falls back to (mamba_state_8b_kernel.py:743-761) is
+ * mamba_ssm.ops.triton.selective_state_update, and the conv step before it is
+ * causal_conv1d.causal_conv1d_update.  These two entry points restate their published behaviour. */
+
+/* One decode step of the selective-state update on a dense state [B,H,P,N] (bf16 / f16 / f32, N
+ * contiguous), in place, fp32 math: dt = softplus(dt + dt_bias), h' = h exp(A dt) + (B dt) x stored
+ * rounded to the state's type, y = <h', C> + D x taken from the fp32 h'; with z the read-out is gated
+ * as that package does it, y * z * sigmoid(z) (lq_mx_state_update multiplies by z alone, as the
+ * reference's MX kernels do, mamba_state_8b_kernel.py:163-165).  Operands as in lq_mx_update_args. */
+typedef struct lq_dense_update_args {
+  void* state;         int64_t state_stride[4];   int32_t state_dtype; /* [B,H,P,N]               */
+  int32_t batch, heads, dim, dstate;
+  const void* x;       int64_t x_stride[3];       int32_t x_dtype;
+  const void* dt;      int64_t dt_stride[3];      int32_t dt_dtype;
+  const void* dt_bias; int64_t dt_bias_stride[2]; int32_t dt_bias_dtype;
+  const void* A;       int64_t A_stride[3];       int32_t A_dtype;
+  const void* B;       int64_t B_stride[3];       int32_t B_dtype;
+  const void* C;       int64_t C_stride[3];       int32_t C_dtype;
+  const void* D;       int64_t D_stride[2];       int32_t D_dtype;
+  const void* z;       int64_t z_stride[3];       int32_t z_dtype;
+  void* out;           int64_t out_stride[3];     int32_t out_dtype;
+  int32_t ngroups;
+  int32_t dt_softplus;
+} lq_dense_update_args;
+
+int lq_dense_state_update(const lq_dense_update_args* args, void* cuda_stream);
+
+/* One decode step of the depthwise causal convolution: every channel's window conv_state[b,c,:]
+ * moves one place to the left, x[b,c] enters at the end, out[b,c] = sum_w window[w] weight[c,w]
+ * (+ bias[c]), through SiLU when `silu` is set.  fp32 math, the window stored back in its type. */
+typedef struct lq_conv1d_update_args {
+  void* conv_state;   int64_t state_stride[3]; int32_t state_dtype;  /* [B,C,W], W <= 8           */
+  const void* x;      int64_t x_stride[2];     int32_t x_dtype;      /* [B,C]                     */
+  const void* weight; int64_t weight_stride[2]; int32_t weight_dtype; /* [C,W]                    */
+  const void* bias;   int64_t bias_stride[1];  int32_t bias_dtype;   /* [C] or NULL               */
+  void* out;          int64_t out_stride[2];   int32_t out_dtype;    /* [B,C]                     */
+  int32_t batch, channels, width;
+  int32_t silu;
+} lq_conv1d_update_args;
+
+int lq_causal_conv1d_update(const lq_conv1d_update_args* args, void* cuda_stream);
+
 /* sizeof of an ABI struct as the library was compiled: 0 lq_mx_state, 1 lq_rounding,
- * 2 lq_mx_update_args, 3 lq_int4_cache, 4 lq_int4_decode_args; -1 otherwise. */
+ * 2 lq_mx_update_args, 3 lq_int4_cache, 4 lq_int4_decode_args, 5 lq_dense_update_args,
+ * 6 lq_conv1d_update_args; -1 otherwise. */
 int lq_abi_sizeof(int which);
 const char* lq_last_error_string(void);
 /* Reads (and clears) the device-side status word of the current device: 0, or a bit set: bit 0 a

@@ -58,6 +58,24 @@ class MxUpdateArgs(C.Structure):
     )
 
 
+class DenseUpdateArgs(C.Structure):
+    _fields_ = (
+        [("state", C.c_void_p), ("state_stride", C.c_int64 * 4), ("state_dtype", C.c_int32),
+         ("batch", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("dstate", C.c_int32)]
+        + _operand("x", 3) + _operand("dt", 3) + _operand("dt_bias", 2) + _operand("A", 3) + _operand("B", 3)
+        + _operand("C", 3) + _operand("D", 2) + _operand("z", 3) + _operand("out", 3)
+        + [("ngroups", C.c_int32), ("dt_softplus", C.c_int32)]
+    )
+
+
+class Conv1dUpdateArgs(C.Structure):
+    _fields_ = (
+        [("conv_state", C.c_void_p), ("state_stride", C.c_int64 * 3), ("state_dtype", C.c_int32)]
+        + _operand("x", 2) + _operand("weight", 2) + _operand("bias", 1) + _operand("out", 2)
+        + [("batch", C.c_int32), ("channels", C.c_int32), ("width", C.c_int32), ("silu", C.c_int32)]
+    )
+
+
 class Int4Cache(C.Structure):
     _fields_ = [
         ("k_packed", C.c_void_p), ("v_packed", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
@@ -112,8 +130,10 @@ def lib() -> C.CDLL:
     l.lq_int4_decode_workspace_bytes.restype = C.c_size_t
     l.lq_int4_decode_auto_splits.argtypes = [C.c_int32] * 3
     l.lq_int4_decode_auto_splits.restype = C.c_int32
+    l.lq_dense_state_update.argtypes = [C.POINTER(DenseUpdateArgs), C.c_void_p]
+    l.lq_causal_conv1d_update.argtypes = [C.POINTER(Conv1dUpdateArgs), C.c_void_p]
     l.lq_abi_sizeof.argtypes = [C.c_int]
-    for which, struct in enumerate((MxState, Rounding, MxUpdateArgs, Int4Cache, Int4DecodeArgs)):
+    for which, struct in enumerate((MxState, Rounding, MxUpdateArgs, Int4Cache, Int4DecodeArgs, DenseUpdateArgs, Conv1dUpdateArgs)):
         if l.lq_abi_sizeof(which) != C.sizeof(struct):
             raise RuntimeError(f"{LIB_PATH}: struct {struct.__name__} is {l.lq_abi_sizeof(which)} bytes in the library, "
                                f"{C.sizeof(struct)} in the binding; rebuild the library")

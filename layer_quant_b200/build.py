@@ -17,7 +17,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "liblayer_quant_b200.so"
-SOURCES = ["lq_api.cu", "lq_mx_state.cu", "lq_int4_kv.cu"]
+SOURCES = ["lq_api.cu", "lq_mx_state.cu", "lq_int4_kv.cu", "lq_dense_state.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

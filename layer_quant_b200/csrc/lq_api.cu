@@ -34,6 +34,8 @@ LQ_EXPORT int lq_abi_sizeof(int which) {
     case 2: return (int)sizeof(lq_mx_update_args);
     case 3: return (int)sizeof(lq_int4_cache);
     case 4: return (int)sizeof(lq_int4_decode_args);
+    case 5: return (int)sizeof(lq_dense_update_args);
+    case 6: return (int)sizeof(lq_conv1d_update_args);
     default: return -1;
   }
 }

@@ -15,6 +15,8 @@ dependency of the reference (Triton, ``triton/language/random.py``; the referenc
 torch==2.8.0 which ships triton 3.4.x, the fixtures were generated with triton 3.6.0);
 its published algorithm (Philox4x32-10, Salmon et al. 2011) is restated in
 ``oracle/philox.py`` and pinned by known-answer words in the same fixtures.
+``oracle/dense_state.py`` (the unquantised baselines, third-party mamba-ssm / causal-conv1d
+behaviour) is the one part whose parity is unpinned; its header says why.
 """
 from .philox import philox4x32_10, tl_randint, tl_rand, words_to_uniform  # noqa: F401
 from .mx_codec import (  # noqa: F401
@@ -26,3 +28,4 @@ from .int4_kv import (  # noqa: F401
     int4_encode, int4_decode, int4_pack_nibbles, int4_unpack_nibbles, int4_quant_dequant,
     int4_decode_attention, decode_attention_mask,
 )
+from .dense_state import dense_state_update, causal_conv1d_update  # noqa: F401
