@@ -159,7 +159,7 @@ def main() -> int:
     ap.add_argument("--rng", default="layered", choices=["reference", "layered"],
                     help="random stream of the headline number (both are always reported)")
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn"],
+    ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn", "bf16"],
                     help="run only one small kernel case (for ncu captures): plain launches, no graph, no sweep")
     ap.add_argument("--case-batch", type=int, default=64)
     ap.add_argument("--case-ctx", type=int, default=8192)
@@ -258,6 +258,13 @@ def main() -> int:
             plan = ia.Int4DecodePlan(q, c, ctx, 32, k_new=kn, v_new=vn)
             fn = plan.launch
             nbytes = attn_bytes(cb, ctx)
+        elif args.case == "bf16":
+            from layer_quant_b200 import dense_state
+            st = torch.randn(cb, HEADS, DIM, DSTATE, generator=gen, device=dev).mul_(0.5).to(torch.bfloat16)
+            o = make_layers(cb, 1, 8)[0][1]
+            fn = lambda: dense_state.selective_state_update(st, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"],
+                                                            dt_softplus=True, out=o["out"])
+            nbytes = BF16_BYTES_PER_SEQ_LAYER * cb
         else:
             bits = 8 if args.case == "mx8" else 4
             lay = make_layers(cb, 1, bits)

@@ -3,10 +3,13 @@
 //
 // Both are plain HBM streaming kernels: the state update reads and writes every state value once
 // (4 bytes per value for a 16-bit state), so the only design question is bytes in flight.  One CTA
-// owns `hpc` consecutive heads of one (batch, B/C group) as the MX kernel does; a lane owns one
-// 16-value block of FOUR rows per iteration and issues all of their loads (8 x 16 B for a 16-bit
-// state) before the first use, which with four resident CTAs keeps about 64 KB per SM in flight.
+// owns `hpc` consecutive heads of one (batch, B/C group) as the MX kernel does and a lane owns one
+// 16-value block of a row.  Aligned states go through a ring of cp.async stages in shared memory in
+// which every thread copies exactly the bytes it will itself consume, so the ring needs no barrier,
+// only cp.async.wait_group: seven passes (28 KB) per CTA are in flight while one is computed.
+// States that are not 16-byte aligned take the register path (four rows' loads issued before use).
 #include <algorithm>
+#include <cmath>
 
 #include "lq_ssm_operands.cuh"
 
@@ -99,6 +102,50 @@ __device__ __forceinline__ void dense_store16(void* base, int64_t off, bool vec,
   }
 }
 
+// h' = h exp(A dt) + B (dt x) on one 16-value block, and the block's share of <h', C>
+struct DenseRowCtx {
+  const lq_dense_update_args* a;
+  const DenseDerived* d;
+  int b, n0;
+};
+__device__ __forceinline__ float dense_row_update(const DenseRowCtx& c, float (&hv)[16], const float (&Bv)[16], const float (&Cv)[16],
+                                                  int h, int p, float xv, float dt_h, float dA_h) {
+  const lq_dense_update_args& a = *c.a;
+  if (c.d->dt_uniform && c.d->a_scalar) {
+    const float dtx = dt_h * xv;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
+  } else {
+    float dt = dt_h;
+    if (!c.d->dt_uniform) {
+      dt = load_as_float(a.dt, c.b * a.dt_stride[0] + h * a.dt_stride[1] + p * a.dt_stride[2], a.dt_dtype);
+      if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0] + p * a.dt_bias_stride[1], a.dt_bias_dtype);
+      if (a.dt_softplus) dt = softplus_ref(dt);
+    }
+    const float dtx = dt * xv;
+    if (c.d->a_scalar) {
+      const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + Bv[i] * dtx;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (c.n0 + i) * a.A_stride[2], a.A_dtype);
+        hv[i] = hv[i] * expf(Ai * dt) + Bv[i] * dtx;
+      }
+    }
+  }
+  float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    y0 = fmaf(hv[i], Cv[i], y0);
+    y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
+    y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
+    y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
+  }
+  return (y0 + y1) + (y2 + y3);
+}
+
 // gridDim.x = batch * (heads / hpc)
 template <int DT>
 __global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_kernel(const lq_dense_update_args a, const DenseDerived d) {
@@ -139,7 +186,7 @@ __global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_kernel(co
   float Bv[16], Cv[16];
   load_bc16(a.B, a.B_stride, a.B_dtype, b, grp, n0, Bv);
   load_bc16(a.C, a.C_stride, a.C_dtype, b, grp, n0, Cv);
-  const bool hoisted = d.dt_uniform && d.a_scalar;
+  const DenseRowCtx rc{&a, &d, b, n0};
   __syncthreads();
 
 #pragma unroll 1
@@ -165,40 +212,225 @@ __global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_kernel(co
         const bool active = p < P;  // uniform over the lanes of a row
         float y = 0.0f;
         if (active) {
-          const float xv = sxh[p];
-          if (hoisted) {
-            const float dtx = dt_h * xv;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) hv[u][i] = hv[u][i] * dA_h + Bv[i] * dtx;
-          } else {
-            const float dt = d.dt_uniform ? dt_h : row_dt(h, p);
-            const float dtx = dt * xv;
-            if (d.a_scalar) {
-              const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) hv[u][i] = hv[u][i] * dA + Bv[i] * dtx;
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
-                hv[u][i] = hv[u][i] * expf(Ai * dt) + Bv[i] * dtx;
-              }
-            }
-          }
-          float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
-#pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            y0 = fmaf(hv[u][i], Cv[i], y0);
-            y1 = fmaf(hv[u][i + 1], Cv[i + 1], y1);
-            y2 = fmaf(hv[u][i + 2], Cv[i + 2], y2);
-            y3 = fmaf(hv[u][i + 3], Cv[i + 3], y3);
-          }
-          y = (y0 + y1) + (y2 + y3);
+          y = dense_row_update(rc, hv[u], Bv, Cv, h, p, sxh[p], dt_h, dA_h);
           dense_store16<DT>(a.state, base + p * a.state_stride[2], vec, hv[u]);
         }
         for (int o = (1 << d.lpr_log2) >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
         if (active && blk == 0) syh[p] = y;
       }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < hpc * P; i += kDenseThreads) {
+    const int hh = i / P, p = i - hh * P, h = h0 + hh;
+    float y = sy[i];
+    if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
+    if (a.z) {
+      const float z = load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
+      y *= z / (1.0f + expf(-z));
+    }
+    store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
+  }
+}
+
+// The aligned path.  Shared memory: a ring of kRingBytes, then the x / y / dt staging.  A stage holds one
+// pass of the CTA; inside it every warp has its own 32 * CH 16-byte chunks (CH = chunks per 16-value
+// block: 2 for a 16-bit state, 4 for fp32), in the order they have in the warp's rows.  Lane l copies
+// chunks l, 32 + l, ... (contiguous 512 B per instruction, whole sectors) and consumes the CH chunks of
+// its own block, so a warp synchronises with itself only (cp.async.wait_group + __syncwarp); results
+// go back through the same chunks to leave with contiguous 16-byte stores.  Chunk c is kept at
+// position c ^ ((c >> 3) & 3), which makes both access patterns free of bank conflicts.
+constexpr int kRingBytes = 32 * 1024;
+
+__device__ __forceinline__ void dense_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t dense_swz(uint32_t c) { return c ^ ((c >> 3) & 3u); }
+
+// LPR_T: lanes per row when known at compile time (8 for dstate 128), 0 = taken from the arguments.
+template <int DT, int LPR_T>
+__global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kernel(const lq_dense_update_args a, const DenseDerived d) {
+  constexpr int ESZ = DT == LQ_F32 ? 4 : 2;
+  constexpr int CH = ESZ;                                        // 16 * ESZ / 16
+  constexpr int STAGES = kRingBytes / (CH * kDenseThreads * 16);  // 8 or 4
+  constexpr uint32_t kStageBytes = CH * kDenseThreads * 16;
+  extern __shared__ __align__(16) uint8_t smem_ring[];
+  float* sx = reinterpret_cast<float*>(smem_ring + kRingBytes);
+  const int H = a.heads, P = a.dim;
+  const int hpc = d.heads_per_cta;
+  float* sy = sx + hpc * P;
+  float* sdt = sy + hpc * P;
+  float* sdA = sdt + hpc;
+  const int chunks = H / hpc;
+  const int b = blockIdx.x / chunks;
+  const int h0 = (blockIdx.x - b * chunks) * hpc;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lpr_log2 = LPR_T ? (LPR_T == 8 ? 3 : 0) : d.lpr_log2;
+  static_assert(LPR_T == 0 || LPR_T == 8, "specialised for dstate 128 only");
+  const int blk = lane & ((1 << lpr_log2) - 1);
+  const int rsub = lane >> lpr_log2;
+  const int rows_per_warp = 32 >> lpr_log2;
+  const int rows_per_pass = rows_per_warp * (kDenseThreads / 32);
+  const int n0 = blk * 16;
+  const int grp = h0 / (H / a.ngroups);
+  const int prow = warp * rows_per_warp + rsub;          // this thread's row inside a pass
+  const int pph = (P + rows_per_pass - 1) / rows_per_pass;  // passes per head
+  const int npass = hpc * pph;
+  // byte steps of a row: to the next pass of a head, and from a head's last pass to the next head's first
+  const int64_t pass_step = static_cast<int64_t>(rows_per_pass) * a.state_stride[2] * ESZ;
+  const int64_t head_step = a.state_stride[1] * ESZ - (pph - 1) * pass_step;
+  uint8_t* const warp_first = static_cast<uint8_t*>(a.state) +
+                              (b * a.state_stride[0] + h0 * a.state_stride[1] + warp * rows_per_warp * a.state_stride[2]) * ESZ;
+  // the chunks this lane moves: chunk c = 32 k + lane of the warp's rows -> row c / chunks-per-row, column chunk c % ...
+  const int cpr_log2 = lpr_log2 + (CH == 2 ? 1 : 2);
+  int64_t mv_off[CH];
+  int mv_row[CH];
+  uint32_t mv_smem[CH];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const uint32_t c = 32 * k + lane;
+    mv_row[k] = warp * rows_per_warp + static_cast<int>(c >> cpr_log2);
+    mv_off[k] = static_cast<int64_t>(c >> cpr_log2) * a.state_stride[2] * ESZ + (c & ((1u << cpr_log2) - 1)) * 16;
+    mv_smem[k] = warp * (32 * CH * 16) + dense_swz(c) * 16;
+  }
+  uint32_t own_smem[CH];  // the chunks of this lane's own block
+#pragma unroll
+  for (int k = 0; k < CH; ++k) own_smem[k] = warp * (32 * CH * 16) + dense_swz(lane * CH + k) * 16;
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ring));
+
+  // producer cursor: pass `ip` of the CTA = pass `ipp` of its head, whose first row is `irow0`
+  const uint8_t* iptr = warp_first;
+  int ip = 0, ipp = 0, irow0 = 0;
+  auto issue = [&]() {
+    if (ip < npass) {
+      const uint32_t dst = ring + (ip & (STAGES - 1)) * kStageBytes;
+#pragma unroll
+      for (int k = 0; k < CH; ++k)
+        if (irow0 + mv_row[k] < P) dense_cp_async16(dst + mv_smem[k], iptr + mv_off[k]);
+      ++ip;
+      if (++ipp == pph) {
+        ipp = 0;
+        irow0 = 0;
+        iptr += head_step;
+      } else {
+        irow0 += rows_per_pass;
+        iptr += pass_step;
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) issue();
+
+  for (int i = threadIdx.x; i < hpc * P; i += kDenseThreads) {
+    const int hh = i / P, p = i - hh * P;
+    sx[i] = load_as_float(a.x, b * a.x_stride[0] + (h0 + hh) * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
+  }
+  if (d.dt_uniform && threadIdx.x < hpc) {
+    const int h = h0 + threadIdx.x;
+    float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1], a.dt_dtype);
+    if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0], a.dt_bias_dtype);
+    if (a.dt_softplus) dt = softplus_ref(dt);
+    sdt[threadIdx.x] = dt;
+    sdA[threadIdx.x] = d.a_scalar ? expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt) : 0.0f;
+  }
+  float Bv[16], Cv[16];
+  load_bc16(a.B, a.B_stride, a.B_dtype, b, grp, n0, Bv);
+  load_bc16(a.C, a.C_stride, a.C_dtype, b, grp, n0, Cv);
+  const DenseRowCtx rc{&a, &d, b, n0};
+  __syncthreads();
+
+  // consumer cursor
+  uint8_t* cptr = warp_first;
+  int chh = 0, cpp = 0, crow0 = 0;
+  float dt_h = d.dt_uniform ? sdt[0] : 0.0f, dA_h = sdA[0];
+#pragma unroll 1
+  for (int i = 0; i < npass; ++i) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");  // this lane's copies of pass i have landed
+    __syncwarp();                                                           // ... and so have the other lanes'
+    uint8_t* stage = smem_ring + (i & (STAGES - 1)) * kStageBytes;
+    const int crow = crow0 + prow;
+    const bool active = crow < P;
+    float hv[16];
+    if (active) {
+      if (DT == LQ_F32) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 f = *reinterpret_cast<const float4*>(stage + own_smem[k]);
+          hv[4 * k] = f.x; hv[4 * k + 1] = f.y; hv[4 * k + 2] = f.z; hv[4 * k + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint4 q = *reinterpret_cast<const uint4*>(stage + own_smem[k]);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (DT == LQ_BF16) {
+              hv[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
+              hv[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            } else {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+              hv[8 * k + 2 * j] = f.x;
+              hv[8 * k + 2 * j + 1] = f.y;
+            }
+          }
+        }
+      }
+    }
+    issue();  // into the stage of pass i - 1, which the warp left before the __syncwarp above
+    float y = 0.0f;
+    const int srow = chh * P + crow;
+    if (active) {
+      y = dense_row_update(rc, hv, Bv, Cv, h0 + chh, crow, sx[srow], dt_h, dA_h);
+      // the rounded block back into its chunks
+      if (DT == LQ_F32) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          *reinterpret_cast<float4*>(stage + own_smem[k]) = make_float4(hv[4 * k], hv[4 * k + 1], hv[4 * k + 2], hv[4 * k + 3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (DT == LQ_BF16) {
+              const __nv_bfloat162 r = __floats2bfloat162_rn(hv[8 * k + 2 * j], hv[8 * k + 2 * j + 1]);
+              w[j] = *reinterpret_cast<const uint32_t*>(&r);
+            } else {
+              const __half2 r = __floats2half2_rn(hv[8 * k + 2 * j], hv[8 * k + 2 * j + 1]);
+              w[j] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+          }
+          *reinterpret_cast<uint4*>(stage + own_smem[k]) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < CH; ++k)
+      if (crow0 + mv_row[k] < P)
+        *reinterpret_cast<uint4*>(cptr + mv_off[k]) = *reinterpret_cast<const uint4*>(stage + mv_smem[k]);
+    if (LPR_T == 8) {
+      y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
+      y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
+      y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+    } else {
+      for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+    }
+    if (active && blk == 0) sy[srow] = y;
+    if (++cpp == pph) {
+      cpp = 0;
+      crow0 = 0;
+      cptr += head_step;
+      ++chh;
+      if (chh < hpc) {
+        dt_h = d.dt_uniform ? sdt[chh] : 0.0f;
+        dA_h = sdA[chh];
+      }
+    } else {
+      crow0 += rows_per_pass;
+      cptr += pass_step;
     }
   }
   __syncthreads();
@@ -275,21 +507,55 @@ LQ_EXPORT int lq_dense_state_update(const lq_dense_update_args* args, void* cuda
   int dev = 0, sms = 0;
   LQ_CHECK_CUDA(cudaGetDevice(&dev));
   LQ_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  // heads per CTA (all of one B/C group): the divisor that best fills whole waves of resident CTAs while
+  // keeping the CTA's set-up (about six passes' worth) small against its passes
+  const int rows_per_pass = (32 >> d.lpr_log2) * (kDenseThreads / 32);
+  const int pph = (a.dim + rows_per_pass - 1) / rows_per_pass;
+  const double resident = 6.0 * sms;
   int hpc = 1;
-  while (hpc * 2 <= heads_per_group && heads_per_group % (hpc * 2) == 0 &&
-         static_cast<int64_t>(a.batch) * (a.heads / (hpc * 2)) >= 8LL * sms &&
-         static_cast<size_t>(hpc * 2) * (2 * a.dim + 2) * sizeof(float) <= 48 * 1024)
-    hpc *= 2;
+  double best = -1.0;
+  for (int c = 1; c <= heads_per_group; c *= 2) {
+    if (heads_per_group % c != 0 || static_cast<size_t>(c) * (2 * a.dim + 2) * sizeof(float) > 16 * 1024) break;
+    const double waves = static_cast<double>(a.batch) * (a.heads / c) / resident;
+    const double score = waves / std::ceil(waves) * (c * pph) / (c * pph + 6.0);
+    if (score > best) {
+      best = score;
+      hpc = c;
+    }
+  }
   d.heads_per_cta = hpc;
   const size_t smem = static_cast<size_t>(hpc) * (2 * a.dim + 2) * sizeof(float);
   if (smem > 48 * 1024) return fail(LQ_ERR_UNSUPPORTED, "lq_dense_state_update: dim=%d too large", a.dim);
   const int64_t grid = static_cast<int64_t>(a.batch) * (a.heads / hpc);
   LQ_CHECK_ARG(grid <= 0x7FFFFFFFLL, "lq_dense_state_update: batch * heads too large");
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  switch (a.state_dtype) {
-    case LQ_BF16: dense_state_update_kernel<LQ_BF16><<<static_cast<unsigned>(grid), kDenseThreads, smem, st>>>(a, d); break;
-    case LQ_F16: dense_state_update_kernel<LQ_F16><<<static_cast<unsigned>(grid), kDenseThreads, smem, st>>>(a, d); break;
-    default: dense_state_update_kernel<LQ_F32><<<static_cast<unsigned>(grid), kDenseThreads, smem, st>>>(a, d); break;
+  const unsigned g = static_cast<unsigned>(grid);
+  if (d.vector_ok) {
+    const size_t rsmem = kRingBytes + smem;
+#define LQ_DENSE_RING(DT_)                                                                                              \
+  do {                                                                                                                  \
+    if (nblk == 8) {                                                                                                    \
+      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 8>,                                        \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(rsmem)));        \
+      dense_state_update_ring_kernel<DT_, 8><<<g, kDenseThreads, rsmem, st>>>(a, d);                                    \
+    } else {                                                                                                            \
+      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 0>,                                        \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(rsmem)));        \
+      dense_state_update_ring_kernel<DT_, 0><<<g, kDenseThreads, rsmem, st>>>(a, d);                                    \
+    }                                                                                                                   \
+  } while (0)
+    switch (a.state_dtype) {
+      case LQ_BF16: LQ_DENSE_RING(LQ_BF16); break;
+      case LQ_F16: LQ_DENSE_RING(LQ_F16); break;
+      default: LQ_DENSE_RING(LQ_F32); break;
+    }
+#undef LQ_DENSE_RING
+  } else {
+    switch (a.state_dtype) {
+      case LQ_BF16: dense_state_update_kernel<LQ_BF16><<<g, kDenseThreads, smem, st>>>(a, d); break;
+      case LQ_F16: dense_state_update_kernel<LQ_F16><<<g, kDenseThreads, smem, st>>>(a, d); break;
+      default: dense_state_update_kernel<LQ_F32><<<g, kDenseThreads, smem, st>>>(a, d); break;
+    }
   }
   LQ_CHECK_CUDA(cudaGetLastError());
   return LQ_OK;

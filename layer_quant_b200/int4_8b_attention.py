@@ -39,6 +39,9 @@ class Int4KVLayerCache:
     k_scale: torch.Tensor
     v_scale: torch.Tensor
     length: int = 0
+    # Not in the reference: the same length kept on the device (one int64) once prepare_graph_decode has
+    # run; decode steps then read it inside the kernel and advance it on the stream, with no host sync.
+    length_counter: torch.Tensor | None = None
 
 
 def int4_quant_dequant(x: torch.Tensor, group_size: int = 64) -> torch.Tensor:
@@ -131,10 +134,21 @@ def _cache_struct(cache: Int4KVLayerCache, group_size: int) -> _lib.Int4Cache:
     return c
 
 
+def _required_len(positions: torch.Tensor, cache_position, q_len: int) -> int:
+    """max(positions) + 1 as the reference computes it (:667), without the device round trip when the
+    positions are known on the host (no cache_position: arange; a CPU cache_position)."""
+    if cache_position is None:
+        return q_len
+    if cache_position.device.type == "cpu":
+        return int(cache_position.max()) + 1
+    return int(positions.max().item()) + 1
+
+
 def _pack_kv_into_cache(cache: Int4KVLayerCache, key_states: torch.Tensor, value_states: torch.Tensor,
-                        positions: torch.Tensor, group_size: int) -> None:
+                        positions: torch.Tensor, group_size: int, *, known_len: int | None = None) -> None:
     """Quantise ``key_states`` / ``value_states`` [B, Hkv, q_len, D] and write them to cache rows
-    ``positions`` (int64 [q_len], shared by the batch)."""
+    ``positions`` (int64 [q_len], shared by the batch).  ``known_len`` = max(positions) + 1 when the
+    caller already has it (saves the read-back the reference does at :515)."""
     batch, kv_heads, q_len, head_dim = key_states.shape
     if value_states.shape != key_states.shape or value_states.dtype != key_states.dtype:
         raise ValueError("key_states and value_states must agree in shape and dtype")
@@ -149,7 +163,7 @@ def _pack_kv_into_cache(cache: Int4KVLayerCache, key_states: torch.Tensor, value
     vs = (ct.c_int64 * 4)(*value_states.stride())
     _lib.check(_lib.lib().lq_int4_kv_append(ct.byref(c), key_states.data_ptr(), ks, value_states.data_ptr(), vs,
                                            _lib.dtype_code(key_states), positions.data_ptr(), q_len, _lib.stream_ptr(dev)))
-    cache.length = max(cache.length, int(positions.max().item()) + 1)
+    cache.length = max(cache.length, known_len if known_len is not None else int(positions.max().item()) + 1)
 
 
 def _decode_attention_mask(attention_mask: torch.Tensor | None, batch: int, seq_len: int,
@@ -294,6 +308,45 @@ def _append_decode_attention(query_states, key_states, value_states, cache, seq_
     return out
 
 
+def prepare_graph_decode(past_key_value, max_len: int) -> None:
+    """Make the decode steps that follow replayable from a CUDA graph (not in the reference, which
+    reads the position back on the host every step, :515 / :667): every layer cache is grown once to
+    hold ``max_len`` tokens (no reallocation later) and gets its length as a device counter.  From
+    then on a q_len = 1 forward appends at the counter's position, attends over [0, position] and
+    advances the counter on the stream; no ``.item()``, no allocation, arguments that stay valid for
+    every replay.  ``cache.length`` on the host is no longer advanced; ``sync_graph_decode`` reads it
+    back.  A step beyond ``max_len`` is clamped by the kernel and reported by ``lq_device_status``."""
+    caches = _cache_dict(past_key_value)
+    if not caches:
+        raise ValueError("prepare_graph_decode needs the caches of a finished prefill")
+    for idx, cur in list(caches.items()):
+        batch, kv_heads, cap, half = cur.k_packed.shape
+        groups = cur.k_scale.shape[3]
+        if cap < max_len:
+            cur = _ensure_layer_cache(past_key_value, idx, batch, kv_heads, max_len, 2 * half, (2 * half) // groups,
+                                      cur.k_packed.device)
+        cur.length_counter = torch.full((1,), cur.length, device=cur.k_packed.device, dtype=torch.int64)
+        caches[idx] = cur
+
+
+def sync_graph_decode(past_key_value) -> None:
+    """Copy the device-side lengths back into ``cache.length`` (one read-back per layer cache)."""
+    for cur in _cache_dict(past_key_value).values():
+        if cur.length_counter is not None:
+            cur.length = int(cur.length_counter.item())
+
+
+def _graph_decode_step(query_states, key_states, value_states, cache, group_size, attention_mask):
+    if attention_mask is not None:
+        raise NotImplementedError("recorded decode steps take no attention_mask: a mask's length changes every step")
+    advance_seq_len(cache.length_counter)  # the new token's position + 1
+    capacity = cache.k_packed.shape[2]
+    a, out, keep = _decode_args(query_states, cache, capacity, group_size, None, key_states, value_states,
+                                seq_len_counter=cache.length_counter)
+    _lib.check(_lib.lib().lq_int4_decode_attn(ct.byref(a), _lib.stream_ptr(out.device)))
+    return out
+
+
 def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
                            output_attentions=False, use_cache=False, cache_position=None):
     """Replacement ``forward`` of a Nemotron-H attention mixer (no RoPE in this architecture):
@@ -319,8 +372,14 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
     key_states = heads(self.k_proj(hidden_states), self.num_key_value_heads)
     value_states = heads(self.v_proj(hidden_states), self.num_key_value_heads)
 
+    graph_cache = _cache_dict(past_key_value).get(self.layer_idx) if q_len == 1 else None
+    if graph_cache is not None and graph_cache.length_counter is not None:
+        # prepared for recorded decode steps: position = the device-side length, nothing read back
+        attn = _graph_decode_step(query_states, key_states, value_states, graph_cache, group_size, attention_mask)
+        return self.o_proj(attn.reshape(bsz, 1, -1)), None, past_key_value
+
     positions = _positions(cache_position, q_len, hidden_states.device)
-    required_len = int(positions.max().item()) + 1
+    required_len = _required_len(positions, cache_position, q_len)
     layer_cache = _ensure_layer_cache(past_key_value, self.layer_idx, bsz, self.num_key_value_heads, required_len,
                                       self.head_dim, group_size, hidden_states.device)
 
@@ -329,7 +388,7 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
                                         self.num_key_value_groups, group_size, attention_mask=attention_mask)
         return self.o_proj(attn.reshape(bsz, 1, -1)), None, past_key_value
 
-    _pack_kv_into_cache(layer_cache, key_states, value_states, positions, group_size)
+    _pack_kv_into_cache(layer_cache, key_states, value_states, positions, group_size, known_len=required_len)
     k_full = self._int4_kv_repeat_kv(key_states, self.num_key_value_groups)
     v_full = self._int4_kv_repeat_kv(value_states, self.num_key_value_groups)
     causal_mask = attention_mask

@@ -63,6 +63,9 @@ class MambaStateKernelCache:
     step: int = 0
     layout: str = "reference"
     layer: int = 0
+    # Not in the reference: the step count kept on the device (one int64) once prepare_graph_decode has
+    # run; the kernel adds it to ``step`` when it runs, so a recorded launch draws fresh numbers on replay.
+    step_counter: torch.Tensor | None = None
 
     @property
     def state_shape(self) -> tuple[int, int, int, int]:
@@ -314,8 +317,29 @@ def mx_state_selective_update(
     ``h_out`` (fp32 [B,H,P,N]) receives the updated state before requantisation; ``out`` is
     written instead of a fresh tensor.  :class:`MxUpdatePlan` prepares the same call once for
     loops that repeat it."""
-    return MxUpdatePlan(cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus, stochastic=stochastic,
-                        seed=seed, rng_stream=rng_stream, rand_words=rand_words, h_out=h_out, out=out).run()
+    y = MxUpdatePlan(cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus, stochastic=stochastic,
+                     seed=seed, rng_stream=rng_stream, rand_words=rand_words, h_out=h_out, out=out,
+                     step_counter=cache.step_counter).run()
+    if cache.step_counter is not None:
+        advance_step_counter(cache.step_counter)
+    return y
+
+
+def prepare_graph_decode(model) -> None:
+    """Make the state updates of the registered caches replayable from a CUDA graph (not in the
+    reference, whose launch bakes the step in as a compile-time constant, :659): each cache's step
+    moves into a device counter that the kernel reads when it runs and that is advanced on the stream
+    after every update.  ``graph_decode_steps`` reads the counters back."""
+    for cache in getattr(model, "_mamba_decode_state_kernel_caches", {}).values():
+        if cache.step_counter is None:
+            cache.step_counter = torch.full((1,), int(cache.step), dtype=torch.int64, device=cache.q_state.device)
+            cache.step = 0  # the kernel uses step + counter
+
+
+def graph_decode_steps(model) -> dict[int, int]:
+    """{layer: steps taken so far} read back from the device counters of the caches in graph mode."""
+    return {cache.layer: int(cache.step_counter.item())
+            for cache in getattr(model, "_mamba_decode_state_kernel_caches", {}).values() if cache.step_counter is not None}
 
 
 def mx8_state_selective_update(*args, **kwargs) -> torch.Tensor:

@@ -17,9 +17,10 @@ F32 = np.float32
 
 
 def _softplus(x):
+    # fp32 log(1 + exp(x)), the form the reference's kernels use (mamba_state_8b_kernel.py:28-30)
     x = np.asarray(x, dtype=F32)
     with np.errstate(over="ignore"):
-        return np.where(x <= 20.0, np.log1p(np.exp(np.minimum(x, 20.0).astype(F32)), dtype=F32), x).astype(F32)
+        return np.where(x <= F32(20.0), np.log(F32(1.0) + np.exp(x)), x).astype(F32)
 
 
 def dense_state_update(state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False):

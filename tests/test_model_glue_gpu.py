@@ -139,3 +139,75 @@ def test_unregistered_states_fall_through_to_the_original_update(runs):
     B = torch.ones((1, 2, 128), device="cuda", dtype=torch.bfloat16)
     y = shim.selective_state_update(state, x, dt, A, B, B)
     assert torch.allclose(y.float(), torch.full_like(y.float(), 128.0)) and float(state.float().mean()) == 1.0
+
+
+def test_whole_decode_step_replays_from_a_cuda_graph():
+    """INT4 KV + MX8 state decode with the positions and step counts on the device: the whole model step
+    (embedding to logits) is recorded once and replayed for every token; logits must track the eager,
+    host-synchronised run of the same patched model, and the caches must end up at the same lengths."""
+    from layer_quant_b200 import int4_8b_attention as ia
+    from layer_quant_b200 import mamba_state_8b_kernel as mk
+    from layer_quant_b200 import _lib
+    original_ssu = shim.selective_state_update
+    for name in ("_mx_state_kernel_patched", "_mx_state_kernel_original"):
+        if hasattr(shim, name):
+            delattr(shim, name)
+    try:
+        model, cfg = _model(seed=3)
+        ids = torch.randint(0, cfg.vocab_size, (BATCH, CTX + STEPS + 1), generator=torch.Generator().manual_seed(4)).cuda()
+        mamba = [i for i, k in enumerate(cfg.hybrid_override_pattern) if k == "M"]
+        ia.patch_nemotron_h_attention_int4_kv(model, group_size=32)
+        mk.patch_nemotron_h_mamba_decode_state_kernel(model, 16, stochastic=False, seed=0)
+        eager, eager_cache = _decode(model, cfg, ids, {i: "mx8" for i in mamba})
+
+        shim._mamba_decode_state_kernel_caches = {}
+        cache = shim.HybridMambaAttentionDynamicCache(cfg, BATCH, torch.bfloat16, device=ids.device)
+        token = torch.zeros((BATCH, 1), dtype=ids.dtype, device=ids.device)
+        with torch.inference_mode():
+            model(ids[:, :CTX], cache_params=cache, cache_position=torch.arange(CTX, device=ids.device))
+            mk.register_mamba_state_kernel_caches(model, cache, {i: "mx8" for i in mamba})
+            ia.prepare_graph_decode(cache, CTX + STEPS)
+            mk.prepare_graph_decode(model)
+            # one step outside the recording (allocates the scratch), undone on the device-side counters
+            snap = [(c.length_counter.clone()) for c in ia._cache_dict(cache).values()]
+            snap_state = [(k.q_state.clone(), k.shared_exp.clone(), k.micro_exp.clone(), k.step_counter.clone())
+                          for k in model._mamba_decode_state_kernel_caches.values()]
+            conv = [c.clone() for c in cache.conv_states]
+            token.copy_(ids[:, CTX:CTX + 1])
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                model(token, cache_params=cache)
+            torch.cuda.current_stream().wait_stream(side)
+            for c, n in zip(ia._cache_dict(cache).values(), snap):
+                c.length_counter.copy_(n)
+            for k, (q, e, m, st) in zip(model._mamba_decode_state_kernel_caches.values(), snap_state):
+                k.q_state.copy_(q), k.shared_exp.copy_(e), k.micro_exp.copy_(m), k.step_counter.copy_(st)
+            for dst, src in zip(cache.conv_states, conv):
+                dst.copy_(src)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = model(token, cache_params=cache).logits
+            got = []
+            for s in range(STEPS):
+                token.copy_(ids[:, CTX + s:CTX + s + 1])
+                graph.replay()
+                got.append(static_logits[:, -1].float().clone())
+        torch.cuda.synchronize()
+        got = torch.stack(got, dim=1)
+        scale = float(eager.abs().max())
+        assert float((got - eager).abs().max()) <= 2e-2 * scale, float((got - eager).abs().max()) / scale
+        assert _kl(eager, got) < 1e-3
+        ia.sync_graph_decode(cache)
+        assert all(c.length == CTX + STEPS for c in ia._cache_dict(cache).values())
+        assert set(mk.graph_decode_steps(model).values()) == {STEPS}
+        assert _lib.device_status() == 0
+        # the INT4 rows appended by the replays are the rows the eager run appended (same K/V up to MX/attention noise
+        # upstream, so compare the prefill rows exactly and the shapes of the rest)
+        for idx, c in ia._cache_dict(cache).items():
+            ref = ia._cache_dict(eager_cache)[idx]
+            assert torch.equal(c.k_packed[:, :, :CTX], ref.k_packed[:, :, :CTX])
+            assert torch.equal(c.v_scale[:, :, :CTX], ref.v_scale[:, :, :CTX])
+    finally:
+        shim.selective_state_update = original_ssu
+        shim._mamba_decode_state_kernel_caches = {}
