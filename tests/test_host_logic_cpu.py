@@ -181,3 +181,71 @@ def test_exponent_table_matches_oracle_formula():
         f = (bits >> 23).astype(np.int64)
         mine = np.maximum(f - shift + ((bits & 0x7FFFFF) > cut[f]).astype(np.int64), 28)
         assert np.array_equal(mine, e[:, 0].astype(np.int64)), name
+
+
+def test_required_len_without_device_round_trip():
+    from layer_quant_b200 import int4_8b_attention as a
+    cpu = torch.device("cpu")
+    assert a._required_len(a._positions(None, 7, cpu), None, 7) == 7
+    cp = torch.tensor([40, 41, 42])
+    assert a._required_len(a._positions(cp, 3, cpu), cp, 3) == 43
+    with pytest.raises(ValueError, match="prepare_graph_decode needs the caches"):
+        a.prepare_graph_decode(object.__new__(type("Cache", (), {})), 64)
+
+
+def test_recorded_launch_helpers_validate_on_the_host():
+    from layer_quant_b200 import int4_8b_attention as a
+    cache = a._allocate_layer_cache(1, 2, 16, 128, 4, torch.device("cpu"))
+    with pytest.raises(ValueError, match="expects q_len=1"):
+        a.Int4DecodePlan(torch.zeros(1, 8, 2, 128), cache, 4, 32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        a.Int4DecodePlan(torch.zeros(1, 8, 1, 128), cache, 4, 32)
+
+
+def test_unquantised_baselines_validate_on_the_host():
+    from layer_quant_b200 import dense_state as d
+    state = torch.zeros(2, 4, 8, 32)
+    x = torch.zeros(2, 4, 8)
+    A = torch.zeros(4, 8, 32)
+    B = torch.zeros(2, 2, 32)
+    with pytest.raises(ValueError, match="do not match state"):
+        d.selective_state_update(state, x[:, :, :4], x, A, B, B)
+    with pytest.raises(ValueError, match="A .* does not match"):
+        d.selective_state_update(state, x, x, A[:, :, :16], B, B)
+    with pytest.raises(ValueError, match="not a multiple"):
+        d.selective_state_update(state, x, x, A, torch.zeros(2, 3, 32), torch.zeros(2, 3, 32))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        d.selective_state_update(state, x, x, A, B, B)
+    conv = torch.zeros(2, 6, 4)
+    with pytest.raises(NotImplementedError):
+        d.causal_conv1d_update(torch.zeros(2, 6), conv, torch.zeros(6, 4), activation="relu")
+    with pytest.raises(ValueError, match="weight"):
+        d.causal_conv1d_update(torch.zeros(2, 6), conv, torch.zeros(6, 3))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        d.causal_conv1d_update(torch.zeros(2, 6), conv, torch.zeros(6, 4))
+
+
+def test_dense_oracle_against_plain_torch():
+    """The CPU restatement of the unquantised step against an independent torch formulation (fp64)."""
+    rng = np.random.default_rng(0)
+    b, h, p, n, g = 2, 4, 3, 16, 2
+    state = rng.standard_normal((b, h, p, n)).astype(np.float32)
+    x, dt = rng.standard_normal((b, h, p)).astype(np.float32), rng.standard_normal((b, h, p)).astype(np.float32)
+    A = -np.exp(rng.standard_normal((h, p, n))).astype(np.float32)
+    B, C = rng.standard_normal((b, g, n)).astype(np.float32), rng.standard_normal((b, g, n)).astype(np.float32)
+    D, z, bias = rng.random((h, p)).astype(np.float32), rng.standard_normal((b, h, p)).astype(np.float32), rng.random((h, p)).astype(np.float32)
+    hq, y = oracle.dense_state_update(state, x, dt, A, B, C, D, z, bias, True)
+    T = lambda v: torch.from_numpy(v).double()
+    dts = torch.nn.functional.softplus(T(dt) + T(bias))
+    Bh, Ch = T(B).repeat_interleave(h // g, 1)[:, :, None], T(C).repeat_interleave(h // g, 1)[:, :, None]
+    want_h = T(state) * torch.exp(T(A) * dts[..., None]) + Bh * (dts * T(x))[..., None]
+    want_y = ((want_h * Ch).sum(-1) + T(x) * T(D)) * torch.nn.functional.silu(T(z))
+    np.testing.assert_allclose(hq, want_h.numpy(), rtol=2e-5, atol=1e-6)
+    np.testing.assert_allclose(y, want_y.numpy(), rtol=2e-5, atol=2e-5)
+    conv = rng.standard_normal((2, 5, 4)).astype(np.float32)
+    xc, w, bc = rng.standard_normal((2, 5)).astype(np.float32), rng.standard_normal((5, 4)).astype(np.float32), rng.standard_normal(5).astype(np.float32)
+    win, out = oracle.causal_conv1d_update(conv, xc, w, bc, silu=True)
+    seq = torch.cat([T(conv), T(xc)[:, :, None]], -1)  # [B, C, W + 1]
+    want = torch.nn.functional.conv1d(seq, T(w)[:, None], T(bc), groups=5)[:, :, -1]
+    np.testing.assert_allclose(out, torch.nn.functional.silu(want).numpy(), rtol=1e-5, atol=1e-6)
+    assert np.array_equal(win, seq[:, :, 1:].float().numpy())
