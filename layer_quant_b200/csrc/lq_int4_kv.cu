@@ -602,22 +602,24 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kMaxTickets = 65536;
 constexpr size_t kTicketBytes = kMaxTickets * sizeof(int32_t);
 
+// Split count from a cost model fitted to measurements on B200 (times in units of one 64-token tile
+// on one SM, about 0.38 us): an SM works through its CTAs' tiles at the same rate whether one or three
+// CTAs are resident, every CTA adds about five tiles' worth of set-up and merge, a lone CTA per SM
+// cannot hide its set-up behind a neighbour, and every split adds a little merge traffic.
 static int pick_splits(int batch, int kv_heads, int ctx_len) {
   const int ntiles = std::max(1, (ctx_len + kTile - 1) / kTile);
-  const int sms = 3 * sm_count();  // resident CTAs of the decode kernel: three per SM (bf16 queries, up to 4 per kv head)
+  const int sms = sm_count();
   const int64_t base = static_cast<int64_t>(batch) * kv_heads;
   int best = 1;
-  double best_score = -1.0;
+  double best_cost = 1.0e300;
   const int max_splits = std::min(ntiles, 128);
   for (int s = 1; s <= max_splits; ++s) {
     const int tps = (ntiles + s - 1) / s;
     if ((ntiles + tps - 1) / tps != s) continue;  // would leave empty splits
-    const int64_t ctas = base * s;
-    const int64_t waves = (ctas + sms - 1) / sms;
-    double score = static_cast<double>(ctas) / static_cast<double>(waves * sms);  // how full the last wave is
-    score *= static_cast<double>(tps) / (tps + 4.0);  // a CTA pays ~4 tiles' worth of ramp-up and merge
-    if (score > best_score * 1.02) {  // more splits only when they clearly pay: each adds merge traffic
-      best_score = score;
+    const int64_t per_sm = (base * s + sms - 1) / sms;  // CTAs on the busiest SM
+    const double cost = static_cast<double>(per_sm) * (tps + 5.3) + (per_sm == 1 ? 10.5 : 0.0) + 0.05 * s;
+    if (cost < best_cost * 0.999) {  // ties go to fewer splits
+      best_cost = cost;
       best = s;
     }
   }

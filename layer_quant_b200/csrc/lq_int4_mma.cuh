@@ -208,38 +208,23 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
     }
   };
 
-  // ---- fused append: quantise the new K / V row, write it to the cache and into a 16-row tile -------
-  if (do_new) {
-    for (int i = threadIdx.x; i < L::kNewBytes / 16; i += kThreadsM) reinterpret_cast<uint4*>(newtile)[i] = make_uint4(0, 0, 0, 0);
+  // start the ring now: the first tiles travel while the new row is quantised and the Q fragments are built
+  for (int it = 0; it < kStagesM - 1; ++it) {
+    if (it < my_tiles) issue_tile(it);
+    cp_async_commit();
   }
-  __syncthreads();
+
+  // the new row's values are fetched now and quantised after the Q fragments, so that the two sets of
+  // loads are in flight together
+  float xnew[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (do_new && warp < 2) {
     const void* src = warp == 0 ? a.k_new : a.v_new;
     const int64_t* ss = warp == 0 ? a.k_new_stride : a.v_new_stride;
-    float x[4];
-    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      x[i] = load_as_float(src, b * ss[0] + kvh * ss[1] + (lane * 4 + i) * ss[2], a.dtype);
-      amax = fmaxf(amax, fabsf(x[i]));
-    }
-#pragma unroll
-    for (int o = GS / 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float scale = int4_scale(amax);
-    uint32_t half = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) half |= int4_code(x[i], scale) << (4 * i);
-    const int pos = rl.seq_len - 1;
-    uint8_t* gcodes = (warp == 0 ? c.k_packed + kp_base + static_cast<int64_t>(pos) * c.kp_stride[2]
-                                 : c.v_packed + vp_base + static_cast<int64_t>(pos) * c.vp_stride[2]);
-    reinterpret_cast<uint16_t*>(gcodes)[lane] = static_cast<uint16_t>(half);
-    reinterpret_cast<uint16_t*>(newtile + (warp == 0 ? L::kNewKc : L::kNewVc))[lane] = static_cast<uint16_t>(half);  // row 0: no swizzle
-    if ((lane * 4) % GS == 0) {
-      float* gsc = (warp == 0 ? c.k_scale + ks_base + static_cast<int64_t>(pos) * c.ks_stride[2]
-                              : c.v_scale + vs_base + static_cast<int64_t>(pos) * c.vs_stride[2]);
-      gsc[lane * 4 / GS] = scale;
-      reinterpret_cast<float*>(newtile + (warp == 0 ? L::kNewKs : L::kNewVs))[lane * 4 / GS] = scale;
-    }
+    for (int i = 0; i < 4; ++i) xnew[i] = load_as_float(src, b * ss[0] + kvh * ss[1] + (lane * 4 + i) * ss[2], a.dtype);
+  }
+  if (do_new) {
+    for (int i = threadIdx.x; i < L::kNewBytes / 16; i += kThreadsM) reinterpret_cast<uint4*>(newtile)[i] = make_uint4(0, 0, 0, 0);
   }
 
   // ---- Q fragments (A operand of S), in the k order the K unpack produces ------------------------------
@@ -286,6 +271,31 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
       qoff_lo[i] = -136.0f * qs_lo;
     }
   }
+  // ---- fused append: quantise the new K / V row, write it to the cache and into a 16-row tile -------
+  __syncthreads();  // the tile of the new row is zeroed
+  if (do_new && warp < 2) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(xnew[i]));
+#pragma unroll
+    for (int o = GS / 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float scale = int4_scale(amax);
+    uint32_t half = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) half |= int4_code(xnew[i], scale) << (4 * i);
+    const int pos = rl.seq_len - 1;
+    uint8_t* gcodes = (warp == 0 ? c.k_packed + kp_base + static_cast<int64_t>(pos) * c.kp_stride[2]
+                                 : c.v_packed + vp_base + static_cast<int64_t>(pos) * c.vp_stride[2]);
+    reinterpret_cast<uint16_t*>(gcodes)[lane] = static_cast<uint16_t>(half);
+    reinterpret_cast<uint16_t*>(newtile + (warp == 0 ? L::kNewKc : L::kNewVc))[lane] = static_cast<uint16_t>(half);  // row 0: no swizzle
+    if ((lane * 4) % GS == 0) {
+      float* gsc = (warp == 0 ? c.k_scale + ks_base + static_cast<int64_t>(pos) * c.ks_stride[2]
+                              : c.v_scale + vs_base + static_cast<int64_t>(pos) * c.vs_stride[2]);
+      gsc[lane * 4 / GS] = scale;
+      reinterpret_cast<float*>(newtile + (warp == 0 ? L::kNewKs : L::kNewVs))[lane * 4 / GS] = scale;
+    }
+  }
+
   const float scale_sm = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
 
   // O^T accumulators: m-tile (chunk i, half sp) has row g = dim 32 i + 4 g + 2 sp and row g + 8 = that
@@ -437,11 +447,7 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
     }
   };
 
-  // ---- main loop: 4-stage cp.async ring ------------------------------------------------------------------
-  for (int it = 0; it < kStagesM - 1; ++it) {
-    if (it < my_tiles) issue_tile(it);
-    cp_async_commit();
-  }
+  // ---- main loop: 4-stage cp.async ring (its first stages were started before the prologue) --------
   for (int it = 0; it < my_tiles; ++it) {
     cp_async_wait<kStagesM - 2>();
     __syncthreads();  // tile `it` has landed for everyone; everyone is done with tile it - 1
