@@ -104,6 +104,14 @@ __device__ __forceinline__ void mma_bf16_from(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
 
+// 8x8 matrix of 16-bit elements held one row per lane group (lane 4 r + c holds row r, columns 2c, 2c+1),
+// transposed across the warp
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); }
 
 // G consecutive fp32 scales of one token from shared memory (one vector load)
@@ -151,14 +159,15 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;  // mma fragment coordinates: row / column group
-  // Rows of the S fragments.  Up to four query heads per kv head: rows 4..7 repeat rows 0..3, so that
-  // lane row g holds the scores of head g & 3 and the O^T product below can take the bf16 hi part of
-  // P * v_scale from rows 0..3 and the lo part from rows 4..7 as the eight columns of ONE n-tile.
-  // Eight heads: rows are heads, hi and lo parts go to two n-tiles.
+  // Head columns.  Both products put the heads on the n side (8 columns).  Up to four query heads per kv
+  // head: columns 4..7 repeat columns 0..3, so that the O^T product can take the bf16 hi part of
+  // P * v_scale from columns 0..3 and the lo part from columns 4..7 of ONE n-tile.  Eight heads: columns
+  // are heads, hi and lo parts go to two n-tiles.  In the Q^T fragments (B operand) column n = g; in the
+  // accumulators a lane owns columns 2t and 2t + 1.
   constexpr bool DUP = R <= 4;
   constexpr int NT = DUP ? 1 : 2;
   const int hrow = DUP ? (g & 3) : g;
-  const bool is_lo = DUP && g >= 4;
+  const bool is_lo = DUP && t >= 2;
   const uint32_t lo_mul = is_lo ? 65536u : 0u, lo_mask = is_lo ? 0xFFFF0000u : 0u;
   const bool fused_new = a.k_new != nullptr;
   uint8_t* newtile = smem + kStagesM * L::kStage;
@@ -271,6 +280,14 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
       qoff_lo[i] = -136.0f * qs_lo;
     }
   }
+  // accumulator start values of this lane's two columns (the sums live in the lanes of row g = column)
+  float qstart[4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float v = QSPLIT ? qoff[i] + qoff_lo[QSPLIT ? i : 0] : qoff[i];
+    qstart[i][0] = __shfl_sync(0xFFFFFFFFu, v, 8 * t);      // lane (g = 2t, t = 0)
+    qstart[i][1] = __shfl_sync(0xFFFFFFFFu, v, 8 * t + 4);  // lane (g = 2t + 1, t = 0)
+  }
   // ---- fused append: quantise the new K / V row, write it to the cache and into a 16-row tile -------
   __syncthreads();  // the tile of the new row is zeroed
   if (do_new && warp < 2) {
@@ -310,75 +327,87 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[i][sp][nt][e] = 0.0f;
   const int col_head0 = DUP ? ((2 * t) & 3) : 2 * t;  // head of accumulator column 2t (column 2t+1: the next head)
-  float m_run = kNegBigM, l_run = 0.0f;  // head hrow of this warp's token stream (l: this lane's share)
+  float m_run[2] = {kNegBigM, kNegBigM}, l_run[2] = {0.0f, 0.0f};  // this lane's two columns (l: this lane's share)
 
   // Per-thread offsets inside a tile for this warp's 16 rows (row0 = 16 * warp; 0 for the new-row tile):
   // ldmatrix row addresses for K (two 8-token halves) and V (two chunk pairs), and the scale rows of
-  // the four tokens this thread owns in the S fragments (rows 8 j + 2 t + e).
-  auto make_offsets = [&](int row0, uint32_t (&koff)[2], uint32_t (&voff)[2], uint32_t (&soff)[2][2]) {
+  // the two tokens this thread owns in the S^T fragments (rows g and g + 8).
+  auto make_offsets = [&](int row0, uint32_t (&koff)[2], uint32_t (&voff)[2], uint32_t (&soff)[2]) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) koff[j] = swz(row0 + 8 * j + (lane & 7), lane >> 3);
     const int mtx = lane >> 3;
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) voff[cp] = swz(row0 + 8 * (mtx & 1) + (lane & 7), 2 * cp + (mtx >> 1));
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) soff[j][e] = (row0 + 8 * j + 2 * t + e) * G * 4;
+    for (int r = 0; r < 2; ++r) soff[r] = (row0 + g + 8 * r) * G * 4;
   };
-  uint32_t koff[2], voff[2], soff[2][2];
+  uint32_t koff[2], voff[2], soff[2];
   make_offsets(16 * warp, koff, voff, soff);
 
   // One 16-token step of this warp.  kc / vc / ksc / vsc: shared-memory addresses of the tile's parts.
   // FULL: all 16 rows hold tokens (no validity selects); otherwise the first `valid` rows do, and the
   // rest were zero-filled by the staging copies (codes 0, scales 0), so they only need masking in S.
   auto step16 = [&](auto full_tag, uint32_t kc, uint32_t vc, const uint8_t* ksc, const uint8_t* vsc, const uint32_t (&ko)[2],
-                    const uint32_t (&vo)[2], const uint32_t (&so)[2][2], int valid, int tok_first) {
+                    const uint32_t (&vo)[2], const uint32_t (&so)[2], int valid, int tok_first) {
     constexpr bool FULL = decltype(full_tag)::value;
-    // S = Q K^T, one accumulator per 16-byte chunk; scores of head g for tokens 8 j + 2 t + e of the step
-    float sv[2][2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      float sacc[4][4];
-      uint32_t kr[4];
-      ldmatrix_x4(kr, kc + ko[j]);
+    // S^T = K Q^T: M = the 16 tokens (rows g and g + 8), N = head columns, K = 16 dims per mma; the unpacked
+    // codes are the A operand, the Q^T fragments stay in registers.  One accumulator per 16-byte chunk.
+    float sacc[4][4];
+    {
+      uint32_t kr0[4], kr1[4];
+      ldmatrix_x4(kr0, kc + ko[0]);
+      ldmatrix_x4(kr1, kc + ko[1]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float c_lo = QSPLIT ? qoff_lo[QSPLIT ? i : 0] : 0.0f;
-        const uint32_t w = kr[i];
-        mma_bf16_from(sacc[i], qa[i][0][0], QSPLIT ? ql[QSPLIT ? i : 0][0][0] : 0u, qa[i][0][1],
-                      QSPLIT ? ql[QSPLIT ? i : 0][0][1] : 0u, nib_pair_biased(w), nib_pair_biased(w >> 4), qoff[i], qoff[i], c_lo,
-                      c_lo);
-        mma_bf16(sacc[i], qa[i][1][0], QSPLIT ? ql[QSPLIT ? i : 0][1][0] : 0u, qa[i][1][1], QSPLIT ? ql[QSPLIT ? i : 0][1][1] : 0u,
-                 nib_pair_biased(w >> 8), nib_pair_biased(w >> 12));
-      }
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float sc[G];
-        load_scales(ksc + so[j][e], sc);
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], QSPLIT ? sacc[i][e] + sacc[i][e + 2] : sacc[i][e], sum);
-        sum *= scale_sm;
-        const int rr = 8 * j + 2 * t + e;
-        if (HAS_MASK) {
-          const int n = tok_first + rr;
-          sum += ((FULL || rr < valid) && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
-        }
-        sv[j][e] = (FULL || rr < valid) ? sum : -INFINITY;
+        const uint32_t w0 = kr0[i], w1 = kr1[i];
+        mma_bf16_from(sacc[i], nib_pair_biased(w0), nib_pair_biased(w1), nib_pair_biased(w0 >> 4), nib_pair_biased(w1 >> 4),
+                      qa[i][0][0], qa[i][0][1], qstart[i][0], qstart[i][1], qstart[i][0], qstart[i][1]);
+        if (QSPLIT)
+          mma_bf16(sacc[i], nib_pair_biased(w0), nib_pair_biased(w1), nib_pair_biased(w0 >> 4), nib_pair_biased(w1 >> 4),
+                   ql[QSPLIT ? i : 0][0][0], ql[QSPLIT ? i : 0][0][1]);
+        mma_bf16(sacc[i], nib_pair_biased(w0 >> 8), nib_pair_biased(w1 >> 8), nib_pair_biased(w0 >> 12), nib_pair_biased(w1 >> 12),
+                 qa[i][1][0], qa[i][1][1]);
+        if (QSPLIT)
+          mma_bf16(sacc[i], nib_pair_biased(w0 >> 8), nib_pair_biased(w1 >> 8), nib_pair_biased(w0 >> 12),
+                   nib_pair_biased(w1 >> 12), ql[QSPLIT ? i : 0][1][0], ql[QSPLIT ? i : 0][1][1]);
       }
     }
-    // online softmax; the running max of a head is shared by its four lanes.  Rows g >= R carry zeros
-    // (their Q rows are zero): they run along harmlessly and are never read.
-    const float smax = fmaxf(fmaxf(sv[0][0], sv[0][1]), fmaxf(sv[1][0], sv[1][1]));
-    if (__any_sync(0xFFFFFFFFu, smax > m_run + kSlackM)) {
-      float rm = fmaxf(smax, __shfl_xor_sync(0xFFFFFFFFu, smax, 1));
-      rm = fmaxf(rm, __shfl_xor_sync(0xFFFFFFFFu, rm, 2));
-      const float m_new = fmaxf(m_run, rm);
-      const float alpha = fast_exp2(m_run - m_new);
-      l_run *= alpha;
-      const float alpha0 = __shfl_sync(0xFFFFFFFFu, alpha, 4 * col_head0);  // the factors of this thread's two columns
-      const float alpha1 = __shfl_sync(0xFFFFFFFFu, alpha, 4 * col_head0 + 4);
+    // scores of tokens g (r = 0) and g + 8 (r = 1) for this lane's two columns
+    float sv[2][2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float sc[G];
+      load_scales(ksc + so[r], sc);
+      const int rr = g + 8 * r;
+      float bias = 0.0f;
+      if (HAS_MASK) {
+        const int n = tok_first + rr;
+        bias = ((FULL || rr < valid) && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
+      }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], sacc[i][2 * r + cc], sum);
+        sum *= scale_sm;
+        if (HAS_MASK) sum += bias;
+        sv[r][cc] = (FULL || rr < valid) ? sum : -INFINITY;
+      }
+    }
+    // online softmax per column; the running max of a column is shared by the eight lanes that hold it.
+    // Columns without a head (zero Q) run along harmlessly and are never read.
+    const float smax0 = fmaxf(sv[0][0], sv[1][0]), smax1 = fmaxf(sv[0][1], sv[1][1]);
+    if (__any_sync(0xFFFFFFFFu, smax0 > m_run[0] + kSlackM || smax1 > m_run[1] + kSlackM)) {
+      float rm0 = smax0, rm1 = smax1;
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        rm0 = fmaxf(rm0, __shfl_xor_sync(0xFFFFFFFFu, rm0, o));
+        rm1 = fmaxf(rm1, __shfl_xor_sync(0xFFFFFFFFu, rm1, o));
+      }
+      const float n0 = fmaxf(m_run[0], rm0), n1 = fmaxf(m_run[1], rm1);
+      const float alpha0 = fast_exp2(m_run[0] - n0), alpha1 = fast_exp2(m_run[1] - n1);
+      l_run[0] *= alpha0;
+      l_run[1] *= alpha1;
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -390,42 +419,40 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
             oacc[i][sp][nt][2] *= alpha0;
             oacc[i][sp][nt][3] *= alpha1;
           }
-      m_run = m_new;
+      m_run[0] = n0;
+      m_run[1] = n1;
     }
     float pv[2][2];
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int r = 0; r < 2; ++r)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        pv[j][e] = fast_exp2(sv[j][e] - m_run);  // 0 for masked / padded tokens
-        l_run += pv[j][e];
+      for (int cc = 0; cc < 2; ++cc) {
+        pv[r][cc] = fast_exp2(sv[r][cc] - m_run[cc]);  // 0 for masked / padded tokens
+        l_run[cc] += pv[r][cc];
       }
-    float vsv[2][2][G];
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        load_scales(vsc + so[j][e], vsv[j][e]);
-#pragma unroll
-        for (int q = 0; q < G; ++q) vsv[j][e][q] *= pv[j][e];  // P * v_scale per group, kept instead of P and the scales
-      }
-    // B operand of O^T: (P * v_scale)^T per scale group, k = the tokens 2t, 2t+1 (+8), n = row g.  A lane of
-    // rows 0..3 keeps the bf16 rounding of the product, a lane of rows 4..7 the bf16 rounding of what that
-    // left over (one formula: the part taken off is masked to zero on the hi lanes).
+    // B operand of O^T: (P * v_scale)^T per scale group, k = the tokens 2t, 2t+1 (+8), n = column g.  What
+    // this lane has is the other way round (token g / g + 8, columns 2t, 2t+1), so each packed pair goes
+    // through movmatrix.  A lane of columns 0..3 keeps the bf16 rounding of the product, a lane of
+    // columns 4..7 the bf16 rounding of what that left over (one formula: the part taken off is masked
+    // to zero on the hi lanes).
     uint32_t pb[G][2][NT];
 #pragma unroll
-    for (int q = 0; q < G; ++q)
+    for (int r = 0; r < 2; ++r) {
+      float vs[G];
+      load_scales(vsc + so[r], vs);
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float p0 = vsv[j][0][q], p1 = vsv[j][1][q];
+      for (int q = 0; q < G; ++q) {
+        const float p0 = pv[r][0] * vs[q], p1 = pv[r][1] * vs[q];
         const uint32_t hi = pack_bf16x2(p0, p1);
         if (DUP) {
-          pb[q][j][0] = pack_bf16x2(p0 - __uint_as_float(hi * lo_mul), p1 - __uint_as_float(hi & lo_mask));
+          pb[q][r][0] = movmatrix_trans(pack_bf16x2(p0 - __uint_as_float(hi * lo_mul), p1 - __uint_as_float(hi & lo_mask)));
         } else {
-          pb[q][j][0] = hi;
-          pb[q][j][NT - 1] = pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xFFFF0000u));
+          pb[q][r][0] = movmatrix_trans(hi);
+          pb[q][r][NT - 1] =
+              movmatrix_trans(pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xFFFF0000u)));
         }
       }
+    }
     // O^T += V^T (P * v_scale)^T, chunk by chunk: the unpacked codes are the A operand
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
@@ -467,7 +494,7 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
   cp_async_wait<0>();
   __syncthreads();
   if (do_new && warp == 0) {
-    uint32_t ko0[2], vo0[2], so0[2][2];
+    uint32_t ko0[2], vo0[2], so0[2];
     make_offsets(0, ko0, vo0, so0);
     const uint32_t nb = s2u(newtile);
     step16(std::false_type{}, nb + L::kNewKc, nb + L::kNewVc, newtile + L::kNewKs, newtile + L::kNewVs, ko0, vo0, so0, 1,
@@ -475,8 +502,11 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
   }
 
   // ---- merge the warps -------------------------------------------------------------------------------------
-  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
-  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 2);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {  // a column's denominator: over the eight lanes (token rows) that share it
+    l_run[0] += __shfl_xor_sync(0xFFFFFFFFu, l_run[0], o);
+    l_run[1] += __shfl_xor_sync(0xFFFFFFFFu, l_run[1], o);
+  }
   float* s_acc = reinterpret_cast<float*>(smem);  // [warps][R][128], reuses the ring
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -495,9 +525,13 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
         const int dim = 32 * i + 4 * g + 2 * sp + (e >> 1);
         if ((!DUP || t < 2) && head < R) s_acc[(warp * R + head) * kD + dim] = v;
       }
-  if (g < R && t == 0) {
-    s_m[warp][g] = m_run;
-    s_l[warp][g] = l_run;
+  if (g == 0 && (!DUP || t < 2)) {
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc)
+      if (col_head0 + cc < R) {
+        s_m[warp][col_head0 + cc] = m_run[cc];
+        s_l[warp][col_head0 + cc] = l_run[cc];
+      }
   }
   __syncthreads();
   const int hq0 = kvh * R;
