@@ -141,7 +141,7 @@ def test_config0_shape_against_reference_cpu_path():
     assert_out_close(m._decode_attention(q.float().to(dev()), cache, 1024, 4, 32), ref)
 
 
-@pytest.mark.parametrize("gs,ratio", [(16, 4), (64, 4), (128, 2), (32, 1), (32, 2), (64, 8)])
+@pytest.mark.parametrize("gs,ratio", [(16, 4), (64, 4), (128, 2), (32, 1), (32, 2), (64, 8), (32, 8), (128, 1)])
 def test_decode_group_sizes_and_gqa_ratios(gs, ratio):
     m = ia()
     b, hkv, tlen = 3, 2, 333
