@@ -365,6 +365,19 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
     b = b_first + static_cast<int>(hh / static_cast<unsigned>(H));
     h = static_cast<int>(hh % static_cast<unsigned>(H));
   };
+  const uint32_t q_row = nblk * IO::kQBytes, m_row = nblk * IO::kMicroBytes, e_row = nblk;
+  const uint32_t r_first = warp * rows_per_warp + rsub;
+  // this lane's block of its first row; every pass moves all three pointers by a constant
+  uint8_t* qptr = static_cast<uint8_t*>(s.q_state) + (R0 + r_first) * q_row + blk * IO::kQBytes;
+  uint8_t* eptr = s.shared_exp + (R0 + r_first) * e_row + blk;
+  uint8_t* mptr = s.micro_exp + (R0 + r_first) * m_row + blk * IO::kMicroBytes;
+  uint64_t lin = (R0 + r_first) * dstate + n0;
+  uint32_t row = r_first;
+  const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
+                 dl = rows_per_pass * dstate;
+  // the first row's block travels while the operands below are staged
+  MxRaw cur = IO::load_ptr(qptr, eptr, mptr);
+
   for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
     int b, h, p;
     row_coords(i, b, h, p);
@@ -389,19 +402,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
   const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * dstate);
 
-  const uint32_t q_row = nblk * IO::kQBytes, m_row = nblk * IO::kMicroBytes, e_row = nblk;
-  const uint32_t r_first = warp * rows_per_warp + rsub;
-  // this lane's block of its first row; every pass moves all three pointers by a constant
-  uint8_t* qptr = static_cast<uint8_t*>(s.q_state) + (R0 + r_first) * q_row + blk * IO::kQBytes;
-  uint8_t* eptr = s.shared_exp + (R0 + r_first) * e_row + blk;
-  uint8_t* mptr = s.micro_exp + (R0 + r_first) * m_row + blk * IO::kMicroBytes;
-  uint64_t lin = (R0 + r_first) * dstate + n0;
-  uint32_t row = r_first;
-  const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
-                 dl = rows_per_pass * dstate;
   __syncthreads();
 
-  MxRaw cur = IO::load_ptr(qptr, eptr, mptr);
   int u = 0;
 #pragma unroll 1
   while (u < n_units) {
