@@ -35,20 +35,22 @@ struct MxBlockIO {
 
   static constexpr int kMicroBytes = (LAYOUT == LQ_MX_LAYOUT_PACKED) ? 1 : 8;
 
-  // One block through plain pointers (dense states: the caller does the address arithmetic once).
+  // One block through plain pointers (dense states: the caller does the address arithmetic once).  The state
+  // is streamed: loads go to L2 only, which also keeps them coherent with a predecessor's stores when the
+  // kernel was scheduled before that predecessor finished.
   __device__ __forceinline__ static MxRaw load_ptr(const uint8_t* q, const uint8_t* e, const uint8_t* m) {
     MxRaw r;
     if (kNibbles) {
-      const uint2 v = *reinterpret_cast<const uint2*>(q);
+      const uint2 v = __ldcg(reinterpret_cast<const uint2*>(q));
       r.q = make_uint4(v.x, v.y, 0u, 0u);
     } else {
-      r.q = *reinterpret_cast<const uint4*>(q);
+      r.q = __ldcg(reinterpret_cast<const uint4*>(q));
     }
-    r.e = *e;
+    r.e = __ldcg(e);
     if (LAYOUT == LQ_MX_LAYOUT_PACKED) {
-      r.mic = *m;
+      r.mic = __ldcg(m);
     } else {
-      const uint2 mm = *reinterpret_cast<const uint2*>(m);
+      const uint2 mm = __ldcg(reinterpret_cast<const uint2*>(m));
       r.mic = (((mm.x & 0x01010101u) * 0x10204080u) >> 28) | ((((mm.y & 0x01010101u) * 0x10204080u) >> 28) << 4);
     }
     return r;
@@ -131,7 +133,7 @@ struct MxRoundBase {
 
 __device__ __forceinline__ MxRoundBase make_round_base(const lq_rounding& r, uint64_t numel) {
   MxRoundBase b;
-  const uint64_t extra = r.step_counter ? __ldg(reinterpret_cast<const unsigned long long*>(r.step_counter)) : 0ull;
+  const uint64_t extra = r.step_counter ? __ldcg(reinterpret_cast<const unsigned long long*>(r.step_counter)) : 0ull;
   b.offset = r.rng_offset + extra * numel;
   b.wrap32 = b.offset < (1ull << 32) ? 1u : 0u;
   b.step = static_cast<uint32_t>(r.step + extra);
@@ -344,6 +346,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   const uint64_t u0 = static_cast<uint64_t>(blockIdx.x) * d.units_total / gridDim.x;
   const uint64_t u1 = static_cast<uint64_t>(blockIdx.x + 1) * d.units_total / gridDim.x;
   const int n_units = static_cast<int>(u1 - u0);
+  // let the next kernel in the stream be scheduled behind this one (no effect without the launch attribute)
+  asm volatile("griddepcontrol.launch_dependents;");
   if (n_units == 0) return;
   const uint64_t R0 = u0 * rows_per_pass;
   const int n_rows = n_units * rows_per_pass;
@@ -375,6 +379,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   uint32_t row = r_first;
   const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
                  dl = rows_per_pass * dstate;
+  // everything above is arithmetic on the arguments; from here on memory the predecessor may have written is read
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // the first row's block travels while the operands below are staged
   MxRaw cur = IO::load_ptr(qptr, eptr, mptr);
 
@@ -626,10 +632,27 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
     const dim3 grid(static_cast<unsigned>(ctas)), block(kUpdateThreads);
     const size_t smem = sizeof(float) * (2 * max_units * rows_per_pass + 2 * max_heads);
     const MxUpdateDerived& d = dd;
-#define LQ_FAST_LAUNCH(MODE_)                                                                        \
-  do {                                                                                              \
-    if (d.nblk == 8) mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 8><<<grid, block, smem, st>>>(a, d); \
-    else mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 0><<<grid, block, smem, st>>>(a, d);        \
+    // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
+    // running (its CTAs take the slots the predecessor's CTAs leave); it touches no global memory before its
+    // griddepcontrol.wait, which returns once the predecessor has completed and its writes are visible.
+    static const bool pdl = [] {
+      const char* env = getenv("LQ_MX_PDL");
+      return env == nullptr || atoi(env) != 0;
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+#define LQ_FAST_LAUNCH(MODE_)                                                                         \
+  do {                                                                                               \
+    if (d.nblk == 8) cudaLaunchKernelEx(&cfg, mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 8>, a, d); \
+    else cudaLaunchKernelEx(&cfg, mx_state_update_fast_kernel<BITS, LAYOUT, MODE_, 0>, a, d);         \
   } while (0)
     switch (a.rounding.mode) {
       case LQ_ROUND_HALF_UP: LQ_FAST_LAUNCH(LQ_ROUND_HALF_UP); break;
