@@ -248,8 +248,10 @@ __device__ __forceinline__ void dense_cp_async16(uint32_t dst, const void* src) 
 __device__ __forceinline__ uint32_t dense_swz(uint32_t c) { return c ^ ((c >> 3) & 3u); }
 
 // LPR_T: lanes per row when known at compile time (8 for dstate 128), 0 = taken from the arguments.
-template <int DT, int LPR_T>
-__global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kernel(const lq_dense_update_args a, const DenseDerived d) {
+// SIMPLE: dt / dt_bias / A per head only and dim a multiple of the rows of a pass (every Mamba2 decode step):
+// no row guards, no per-row operand reloads.
+template <int DT, int LPR_T, bool SIMPLE>
+__global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_ring_kernel(const lq_dense_update_args a, const DenseDerived d) {
   constexpr int ESZ = DT == LQ_F32 ? 4 : 2;
   constexpr int CH = ESZ;                                        // 16 * ESZ / 16
   constexpr int STAGES = kRingBytes / (CH * kDenseThreads * 16);  // 8 or 4
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kern
       const uint32_t dst = ring + (ip & (STAGES - 1)) * kStageBytes;
 #pragma unroll
       for (int k = 0; k < CH; ++k)
-        if (irow0 + mv_row[k] < P) dense_cp_async16(dst + mv_smem[k], iptr + mv_off[k]);
+        if (SIMPLE || irow0 + mv_row[k] < P) dense_cp_async16(dst + mv_smem[k], iptr + mv_off[k]);
       ++ip;
       if (++ipp == pph) {
         ipp = 0;
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kern
     __syncwarp();                                                           // ... and so have the other lanes'
     uint8_t* stage = smem_ring + (i & (STAGES - 1)) * kStageBytes;
     const int crow = crow0 + prow;
-    const bool active = crow < P;
+    const bool active = SIMPLE || crow < P;
     float hv[16];
     if (active) {
       if (DT == LQ_F32) {
@@ -382,7 +384,22 @@ __global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kern
     float y = 0.0f;
     const int srow = chh * P + crow;
     if (active) {
-      y = dense_row_update(rc, hv, Bv, Cv, h0 + chh, crow, sx[srow], dt_h, dA_h);
+      if (SIMPLE) {
+        const float dtx = dt_h * sx[srow];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
+        float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          y0 = fmaf(hv[i], Cv[i], y0);
+          y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
+          y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
+          y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
+        }
+        y = (y0 + y1) + (y2 + y3);
+      } else {
+        y = dense_row_update(rc, hv, Bv, Cv, h0 + chh, crow, sx[srow], dt_h, dA_h);
+      }
       // the rounded block back into its chunks
       if (DT == LQ_F32) {
 #pragma unroll
@@ -409,7 +426,7 @@ __global__ void __launch_bounds__(kDenseThreads, 6) dense_state_update_ring_kern
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < CH; ++k)
-      if (crow0 + mv_row[k] < P)
+      if (SIMPLE || crow0 + mv_row[k] < P)
         *reinterpret_cast<uint4*>(cptr + mv_off[k]) = *reinterpret_cast<const uint4*>(stage + mv_smem[k]);
     if (LPR_T == 8) {
       y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
@@ -511,7 +528,7 @@ LQ_EXPORT int lq_dense_state_update(const lq_dense_update_args* args, void* cuda
   // keeping the CTA's set-up (about six passes' worth) small against its passes
   const int rows_per_pass = (32 >> d.lpr_log2) * (kDenseThreads / 32);
   const int pph = (a.dim + rows_per_pass - 1) / rows_per_pass;
-  const double resident = 6.0 * sms;
+  const double resident = 4.0 * sms;
   int hpc = 1;
   double best = -1.0;
   for (int c = 1; c <= heads_per_group; c *= 2) {
@@ -532,16 +549,17 @@ LQ_EXPORT int lq_dense_state_update(const lq_dense_update_args* args, void* cuda
   const unsigned g = static_cast<unsigned>(grid);
   if (d.vector_ok) {
     const size_t rsmem = kRingBytes + smem;
+    const bool simple = d.dt_uniform && d.a_scalar && a.dim % rows_per_pass == 0;
 #define LQ_DENSE_RING(DT_)                                                                                              \
   do {                                                                                                                  \
-    if (nblk == 8) {                                                                                                    \
-      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 8>,                                        \
+    if (nblk == 8 && simple) {                                                                                          \
+      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 8, true>,                                  \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(rsmem)));        \
-      dense_state_update_ring_kernel<DT_, 8><<<g, kDenseThreads, rsmem, st>>>(a, d);                                    \
+      dense_state_update_ring_kernel<DT_, 8, true><<<g, kDenseThreads, rsmem, st>>>(a, d);                              \
     } else {                                                                                                            \
-      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 0>,                                        \
+      LQ_CHECK_CUDA(cudaFuncSetAttribute(dense_state_update_ring_kernel<DT_, 0, false>,                                 \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(rsmem)));        \
-      dense_state_update_ring_kernel<DT_, 0><<<g, kDenseThreads, rsmem, st>>>(a, d);                                    \
+      dense_state_update_ring_kernel<DT_, 0, false><<<g, kDenseThreads, rsmem, st>>>(a, d);                             \
     }                                                                                                                   \
   } while (0)
     switch (a.state_dtype) {
