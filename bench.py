@@ -14,8 +14,9 @@ the 126 MB L2, so no launch finds its state cached from the previous step).
             read + written)
   e2e       the same metric through the public Python API with the step's x / dt / B / C copied
             from pinned host memory and y copied back, all inside the timed region: prepared
-            launches (MxUpdatePlan) replayed from a CUDA graph, one copy each way per step
-            (`e2e.per_call` is the plain mx_state_selective_update call per layer)
+            launches (MxUpdatePlan) and the copies, in four pieces of six layers on their own
+            streams, replayed as one CUDA graph per step (`e2e.per_call` is the plain
+            mx_state_selective_update call per layer)
   roofline  the MX8 update kernel against the measured HBM copy bandwidth
   sweep     larger shapes of the same kernels (MX8 / MX4 at batch 256, INT4-KV decode attention
             cells), each as algorithmic GB/s and fraction of the measured peak
@@ -293,8 +294,8 @@ def main() -> int:
     # ---- end to end: host buffers in, host buffer out, through the public calls -------------------------
     # (a) per call: mx_state_selective_update once per layer with fresh copies of its operands, the way the
     #     reference's decode loop calls it; (b) prepared: the step's operands of all layers in ONE pinned host
-    #     buffer -> one copy in, the 24 prepared launches (MxUpdatePlan) replayed from a CUDA graph, one copy
-    #     of all outputs back.  (b) is the number a serving loop gets and is reported as `e2e`.
+    #     buffer, copied in pieces that overlap the 24 prepared launches (MxUpdatePlan), outputs copied back
+    #     piece by piece, everything replayed from a CUDA graph.  (b) is what a serving loop gets: `e2e`.
     shapes = (("x", (B, HEADS, DIM)), ("dt", (B, HEADS)), ("B", (B, GROUPS, DSTATE)), ("C", (B, GROUPS, DSTATE)))
     per_layer = sum(int(np.prod(sh)) for _, sh in shapes)
     host_all = torch.randn(LAYERS * per_layer).to(torch.bfloat16).pin_memory()
@@ -329,12 +330,44 @@ def main() -> int:
     for li, (cache, o) in enumerate(layers8):
         di = views(dev_all, li)
         e2e_layers.append((cache, dict(o, x=di["x"], dt=di["dt"][:, :, None].expand(B, HEADS, DIM), B=di["B"], C=di["C"], out=out_all[li])))
-    replay = make_step(e2e_layers, args.rng)
+    # The step's operands travel in E2E_CHUNKS pieces (6 layers each) on a copy stream while the previous piece is
+    # computed, and each piece's outputs leave on a third stream as soon as its launches are done; copies, the 24
+    # prepared launches and the counter bump are one CUDA graph.
+    E2E_CHUNKS = 4
+    lpc = LAYERS // E2E_CHUNKS
+    e2e_plans = [mk.MxUpdatePlan(cache, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True,
+                                 stochastic=True, seed=0, rng_stream=args.rng, out=o["out"], step_counter=counter)
+                 for cache, o in e2e_layers]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    def e2e_step():
-        dev_all.copy_(host_all, non_blocking=True)
-        replay()
-        host_out_all.copy_(out_all, non_blocking=True)
+    def e2e_body():
+        main = torch.cuda.current_stream(dev)
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        for c in range(E2E_CHUNKS):
+            lo, hi = c * lpc * per_layer, (c + 1) * lpc * per_layer
+            with torch.cuda.stream(s_in):
+                dev_all[lo:hi].copy_(host_all[lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+            main.wait_event(ev)
+            for pl in e2e_plans[c * lpc:(c + 1) * lpc]:
+                pl.run()
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                host_out_all[c * lpc:(c + 1) * lpc].copy_(out_all[c * lpc:(c + 1) * lpc], non_blocking=True)
+        mk.advance_step_counter(counter)
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
+
+    e2e_body()
+    torch.cuda.synchronize(dev)
+    e2e_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(e2e_graph):
+        e2e_body()
+    e2e_step = e2e_graph.replay
 
     sec_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e_value = bytes_step * world * args.steps / sec_e2e / 1e9
@@ -424,8 +457,9 @@ def main() -> int:
             "dtype": "f32", "data": "synthetic", "config": workload_config(world, B, args.rng),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3,
-                    "mode": "one pinned-host -> device copy of the step's x/dt/B/C for all 24 layers, 24 prepared launches "
-                            "(MxUpdatePlan) replayed from a CUDA graph, one device -> pinned-host copy of all y",
+                    "mode": "pinned-host -> device copies of the step's x/dt/B/C in 4 pieces of 6 layers on a copy stream, the 24 "
+                            "prepared launches (MxUpdatePlan), device -> pinned-host copies of each piece's y on a third "
+                            "stream; all of it one CUDA graph per step",
                     "per_call": {"value": bytes_step * world * args.steps / sec_e2e_call / 1e9,
                                  "ms_per_step": sec_e2e_call / args.steps * 1e3,
                                  "mode": "mx_state_selective_update called per layer, 4 copies in + 1 out per call"}},
