@@ -441,6 +441,29 @@ def main() -> int:
                                                   "us_per_launch": round(s / (5 * reps) * 1e6, 1)}
             del caches
             torch.cuda.empty_cache()
+        if rank == 0 and not args.no_cpu_baseline:
+            # BASELINE config 0 on the host cores, the reference's own CPU-runnable path: torch fake-quant of K / V
+            # (int4_quant_dequant, group 32) + scaled_dot_product_attention, batch 1, 1024 tokens; beside it the
+            # (1, 1024) cell above is the same problem on the GPU.
+            import time
+            import torch.nn.functional as F
+            gq = torch.Generator().manual_seed(0)
+            q0 = torch.randn(1, 32, 1, 128, generator=gq).to(torch.bfloat16)
+            k0, v0 = (torch.randn(1, 8, 1024, 128, generator=gq).to(torch.bfloat16) for _ in range(2))
+
+            def cpu_config0():
+                kq = ia.int4_quant_dequant(k0, 32).repeat_interleave(4, dim=1)
+                vq = ia.int4_quant_dequant(v0, 32).repeat_interleave(4, dim=1)
+                return F.scaled_dot_product_attention(q0, kq, vq)
+
+            for _ in range(3):
+                cpu_config0()
+            t0 = time.perf_counter()
+            for _ in range(20):
+                cpu_config0()
+            cpu_ms = (time.perf_counter() - t0) / 20 * 1e3
+            sweep["config0_int4_attn_b1_ctx1024_cpu_torch"] = {"ms_per_call": round(cpu_ms, 3), "threads": torch.get_num_threads(),
+                                                               "gpu_us_per_launch": sweep["int4_attn_b1_ctx1024"]["us_per_launch"]}
 
     # ---- CPU baseline (rank 0, bounded sample) ----------------------------------------------------------------
     cpu = None

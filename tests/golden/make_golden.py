@@ -245,7 +245,7 @@ def gen_attention(out: Path, ia):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a phcool/Layer_Quant checkout (imported, never copied)")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)

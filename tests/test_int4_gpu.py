@@ -162,7 +162,7 @@ def test_decode_masks():
     add = np.zeros((b, 1, 1, tlen), np.float32)
     add[:, :, :, 100:180] = -np.inf
     add[1, :, :, 7] = -3.25
-    add[0, :, :, 0:64] = -np.inf  # a fully masked first tile (the reference returns NaN there)
+    add[0, :, :, 0:64] = -np.inf  # a fully masked first tile (the reference computes inf - inf = NaN there; the kernel gives the softmax over the rest)
     keep2d = np.ones((b, tlen + 5), np.int64)
     keep2d[0, 20:90] = 0
     short = np.zeros((b, 1, 1, 250), np.float32)  # shorter than the context: the tail is masked out
