@@ -647,27 +647,11 @@ static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
   using L = mma::TileLayout<GS>;
   const size_t smem = mma::kStagesM * L::kStage + L::kNewBytes;
   const dim3 grid(p.splits, p.a.cache.kv_heads, p.a.cache.batch), block(mma::kThreadsM);
-  // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
-  // running; it reads no global memory before its griddepcontrol.wait (LQ_INT4_PDL=0 switches this off).
-  static const bool pdl = [] {
-    const char* env = getenv("LQ_INT4_PDL");
-    return env == nullptr || atoi(env) != 0;
-  }();
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
 #define LQ_MMA_LAUNCH(MASK_, SPLIT_)                                                                                \
   do {                                                                                                              \
     LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_>,                           \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                    \
-    LQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_>, p));                  \
+    mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_><<<grid, block, smem, st>>>(p);                                \
   } while (0)
   const bool qsplit = p.a.dtype != LQ_BF16;
   if (p.a.mask) {

@@ -172,9 +172,6 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
   const bool fused_new = a.k_new != nullptr;
   uint8_t* newtile = smem + kStagesM * L::kStage;
 
-  // the next kernel in the stream may be scheduled behind this one; this one touches memory only from here on
-  asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   const RunLengths rl = run_lengths(p);
   const int ntiles = (rl.ctx_len + kTileTok - 1) / kTileTok;
   const int tile_begin = split * rl.tiles_per_split;
