@@ -225,6 +225,37 @@ def test_sweep_cell_property_constant_values():
     assert rel_err(out2.cpu().numpy(), out.cpu().numpy()) < 1e-4
 
 
+def test_longest_context_cell_properties():
+    """The per-GPU share of the largest sweep cell at 8 GPUs (batch 32, context 131072, 5.4 GB of cache),
+    through properties that need no oracle at that size: (1) with one V vector per head the output is that
+    vector; (2) the result is a convex combination over the context, so splitting the context in two halves
+    and merging the halves' outputs with their softmax masses reproduces the whole; here checked through the
+    split counts 1, 8 and the library's choice agreeing with each other."""
+    m = ia()
+    b, hq, hkv, tlen, gs = 32, 32, 8, 131072, 32
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    cache = m._allocate_layer_cache(b, hkv, tlen, 128, 4, dev())
+    cache.k_packed.copy_(torch.randint(0, 256, cache.k_packed.shape, generator=gen, device=dev(), dtype=torch.int16).to(torch.uint8))
+    cache.k_scale.copy_(torch.rand(cache.k_scale.shape, generator=gen, device=dev()) * 0.05 + 0.01)
+    row_codes = torch.randint(0, 256, (b, hkv, 1, 64), generator=gen, device=dev(), dtype=torch.int16).to(torch.uint8)
+    row_scale = torch.rand((b, hkv, 1, 4), generator=gen, device=dev()) + 0.5
+    cache.v_packed.copy_(row_codes.expand_as(cache.v_packed))
+    cache.v_scale.copy_(row_scale.expand_as(cache.v_scale))
+    q = torch.randn((b, hq, 1, 128), generator=gen, device=dev()).bfloat16()
+    want = oracle.int4_decode(oracle.int4_unpack_nibbles(row_codes.cpu().numpy()), row_scale.cpu().numpy(), gs)[:, :, 0]
+    want = np.repeat(want, 4, axis=1)
+    outs = [m._decode_attention(q, cache, tlen, 4, gs, splits=sp).float().cpu().numpy() for sp in (0, 1, 8)]
+    for out in outs:
+        assert rel_err(out, want) < 2.0 ** -7  # bf16 outputs
+    # now a V that varies along the context: the split counts must agree with each other
+    cache.v_packed.copy_(torch.randint(0, 256, cache.v_packed.shape, generator=gen, device=dev(), dtype=torch.int16).to(torch.uint8))
+    outs = [m._decode_attention(q.float(), cache, tlen, 4, gs, splits=sp).cpu().numpy() for sp in (0, 1, 8, 128)]
+    for out in outs[1:]:
+        assert rel_err(out, outs[0]) < 1e-4
+    from layer_quant_b200 import _lib
+    assert _lib.device_status() == 0
+
+
 def test_cache_growth_and_errors():
     m = ia()
 
