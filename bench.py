@@ -150,6 +150,109 @@ def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> 
     }
 
 
+def model_case(args, dev, rank, world):
+    """BASELINE config 4 in this repository's terms: a random-init Nemotron-H-8B-shaped model
+    (layer_quant_b200/nemotron_h_shim.py; projections, norms and MLP are torch library calls) decodes
+    ``--model-steps`` teacher-forced random tokens after a ``--model-prompt``-token prompt, first unpatched (bf16 KV
+    cache, bf16 SSM state through the library's dense-state kernel), then with INT4 KV (group 32) + MX8 state on every
+    Mamba2 layer, its whole decode step replayed from one CUDA graph.  Each rank holds ``--case-batch`` sequences.
+    Prints tokens/s of both runs and the KL divergence of the logits at the checkpoint steps."""
+    import torch
+    import torch.distributed as dist
+    from layer_quant_b200 import int4_8b_attention as ia, mamba_state_8b_kernel as mk, nemotron_8b_decode_eval as ev
+    from layer_quant_b200 import nemotron_h_shim as shim, sharding
+    cfg = shim.nemotron_h_8b_config() if args.model_shape == "8b" else shim.tiny_config()
+    bm, prompt, steps = args.case_batch, args.model_prompt, args.model_steps
+    checkpoints = [c for c in (128, 256, 512, 1024, 2048) if c <= steps] or [steps]
+    torch.manual_seed(0)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        model = shim.NemotronHShimForCausalLM(cfg)
+    torch.set_default_dtype(old)
+    with torch.no_grad():
+        for prm in model.parameters():
+            if prm.dim() > 1:
+                prm.normal_(0.0, 0.02)
+    model.eval()
+    nparams = sum(prm.numel() for prm in model.parameters())
+    ids = torch.randint(0, cfg.vocab_size, (bm, prompt + steps + 1), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
+    mamba_layers, attn_layers, _ = ev.layer_groups(cfg)
+
+    def timed_region(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sharding.barrier()
+        torch.cuda.synchronize(dev)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        sharding.barrier()
+        return sharding.all_reduce_max(e0.elapsed_time(e1) / 1e3, dev)
+
+    def decode(quantised):
+        shim._mamba_decode_state_kernel_caches = {}
+        cache = ev.make_hybrid_cache(model, bm)
+        kept = {}
+        with torch.inference_mode():
+            model(ids[:, :prompt], cache_params=cache, cache_position=torch.arange(prompt), logits_to_keep=1)
+            if not quantised:
+                def run():
+                    for st in range(steps):
+                        pos = prompt + st
+                        out = model(ids[:, pos:pos + 1], cache_params=cache, cache_position=torch.tensor([pos]))
+                        if st + 1 in checkpoints:
+                            kept[st + 1] = out.logits[:, -1].float()
+                return timed_region(run), steps, kept
+            mk.register_mamba_state_kernel_caches(model, cache, {i: "mx8" for i in mamba_layers})
+            ia.prepare_graph_decode(cache, prompt + steps)
+            mk.prepare_graph_decode(model)
+            token = torch.zeros((bm, 1), dtype=ids.dtype, device=dev)
+            token.copy_(ids[:, prompt:prompt + 1])
+            first = model(token, cache_params=cache).logits[:, -1].float()  # step 1, eager (also warms every library up)
+            if 1 in checkpoints:
+                kept[1] = first
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = model(token, cache_params=cache).logits
+
+            def run():
+                for st in range(1, steps):
+                    token.copy_(ids[:, prompt + st:prompt + st + 1])
+                    graph.replay()
+                    if st + 1 in checkpoints:
+                        kept[st + 1] = static_logits[:, -1].float().clone()
+            return timed_region(run), steps - 1, kept
+
+    sec_base, n_base, logits_base = decode(False)
+    ia.patch_nemotron_h_attention_int4_kv(model, group_size=32)
+    mk.RNG_STREAM = "layered"
+    mk.patch_nemotron_h_mamba_decode_state_kernel(model, 16, stochastic=True, seed=0)
+    sec_q, n_q, logits_q = decode(True)
+    from layer_quant_b200 import _lib
+    status = _lib.device_status()
+    kl = {}
+    for c in checkpoints:
+        lp, lq = torch.log_softmax(logits_base[c], -1), torch.log_softmax(logits_q[c], -1)
+        v = (lp.exp() * (lp - lq)).sum(-1).mean()
+        if world > 1:
+            dist.all_reduce(v)
+            v = v / world
+        kl[str(c)] = float(v)
+    if rank == 0:
+        print(json.dumps({
+            "case": "model", "shape": args.model_shape, "params": nparams, "n_gpus": world, "batch_per_gpu": bm,
+            "global_batch": bm * world, "prompt": prompt, "decode_steps": steps,
+            "tokens_per_s_int4kv_mx8_graph": bm * world * n_q / sec_q, "ms_per_step_int4kv_mx8_graph": sec_q / n_q * 1e3,
+            "tokens_per_s_bf16_eager": bm * world * n_base / sec_base, "ms_per_step_bf16_eager": sec_base / n_base * 1e3,
+            "kl_bf16_vs_quantised_at_step": kl, "device_status": status,
+            "note": "random-init weights ~N(0, 0.02), teacher-forced random tokens; projections / norms / MLP are torch "
+                    "library kernels; the bf16 run is launched eagerly (its growing KV cache cannot be recorded)"}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -160,7 +263,10 @@ def main() -> int:
     ap.add_argument("--rng", default="layered", choices=["reference", "layered"],
                     help="random stream of the headline number (both are always reported)")
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn", "bf16"],
+    ap.add_argument("--model-prompt", type=int, default=1024, help="--case model: prompt length")
+    ap.add_argument("--model-steps", type=int, default=2048, help="--case model: decode steps")
+    ap.add_argument("--model-shape", default="8b", choices=["8b", "tiny"], help="--case model: Nemotron-H-8B shape or the test shape")
+    ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn", "bf16", "model"],
                     help="run only one small kernel case (for ncu captures): plain launches, no graph, no sweep")
     ap.add_argument("--case-batch", type=int, default=64)
     ap.add_argument("--case-ctx", type=int, default=8192)
@@ -245,6 +351,8 @@ def main() -> int:
         sharding.barrier()
         return sharding.all_reduce_max(e0.elapsed_time(e1) / 1e3, dev)
 
+    if args.case == "model":
+        return model_case(args, dev, rank, world)
     if args.case:
         # one kernel, a few plain launches on a working set larger than L2 and at most a few GB
         cb = args.case_batch

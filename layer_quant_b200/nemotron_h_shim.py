@@ -1,4 +1,5 @@
-"""A small Nemotron-H-shaped hybrid model in plain torch (TEST INFRASTRUCTURE).
+"""A Nemotron-H-shaped hybrid model in torch, random-init, for running the patch functions and the
+decode kernels inside a model (tests at a small shape, ``bench.py --case model`` at the 8B shape).
 
 It stands in for the HuggingFace remote-code module the reference patches (the checkpoint, its
 modeling file, ``mamba_ssm`` and ``causal_conv1d`` are not available offline): same block layout
@@ -8,7 +9,9 @@ mixers, a module-global ``selective_state_update`` and ``repeat_kv``, and a
 ``patch_nemotron_h_attention_int4_kv``, ``patch_nemotron_h_mamba_decode_state_kernel`` and
 ``register_mamba_state_kernel_caches`` reach for.  Weights are random; the Mamba2 decode step
 follows the public Mamba2 formulation (in_proj -> causal conv1d update -> selective state update
--> gated RMSNorm -> out_proj), attention has no RoPE, the MLP is squared-ReLU.
+-> gated RMSNorm -> out_proj), attention has no RoPE, the MLP is squared-ReLU.  On CUDA the two
+unquantised steps go through the library's baselines (``layer_quant_b200.dense_state``), the
+stand-ins for the third-party kernels the real module imports; on CPU they are plain torch.
 """
 from __future__ import annotations
 
@@ -28,7 +31,14 @@ def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
 
 def selective_state_update(ssm_state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False):
     """Unquantised decode step on a floating-point state [B, H, P, N] (updated in place), fp32 math:
-    the baseline the MX kernels are compared with."""
+    the baseline the MX kernels are compared with (and the module-global symbol their patch replaces)."""
+    if ssm_state.is_cuda and z is None:
+        from . import dense_state
+        return dense_state.selective_state_update(ssm_state, x, dt, A, B, C, D=D, dt_bias=dt_bias, dt_softplus=dt_softplus)
+    return selective_state_update_torch(ssm_state, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus)
+
+
+def selective_state_update_torch(ssm_state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False):
     batch, nheads, dim, dstate = ssm_state.shape
     dt = dt.float()
     if dt_bias is not None:
@@ -103,13 +113,17 @@ class Mamba2Mixer(nn.Module):
         batch = hs.shape[0]
         gate, xbc, dt = self.in_proj(hs).split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)
         conv_state = cache_params.conv_states[self.layer_idx]
-        conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
-        conv_state[:, :, -1] = xbc
-        xbc = F.silu((conv_state.float() * self.conv1d.weight.squeeze(1).float()).sum(-1) + self.conv1d.bias.float()).to(hs.dtype)
+        if hs.is_cuda:
+            from . import dense_state
+            xbc = dense_state.causal_conv1d_update(xbc, conv_state, self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
+        else:
+            conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+            conv_state[:, :, -1] = xbc
+            xbc = F.silu((conv_state.float() * self.conv1d.weight.squeeze(1).float()).sum(-1) + self.conv1d.bias.float()).to(hs.dtype)
         x, B, C = xbc.split([self.intermediate_size, self.n_groups * self.ssm_state_size, self.n_groups * self.ssm_state_size], dim=-1)
         A = -torch.exp(self.A_log.float())[:, None, None].expand(-1, self.head_dim, self.ssm_state_size)
         y = module.selective_state_update(  # looked up at call time: this is the symbol the MX patch replaces
-            cache_params.ssm_states[self.layer_idx], x.view(batch, self.num_heads, self.head_dim),
+            cache_params.ssm_states[self.layer_idx], x.reshape(batch, self.num_heads, self.head_dim),
             dt[:, :, None].expand(-1, -1, self.head_dim), A, B.view(batch, self.n_groups, -1), C.view(batch, self.n_groups, -1),
             self.D[:, None].expand(-1, self.head_dim), z=None, dt_bias=self.dt_bias[:, None].expand(-1, self.head_dim),
             dt_softplus=True)
@@ -195,11 +209,23 @@ class NemotronHShimForCausalLM(nn.Module):
     def device(self):
         return self.lm_head.weight.device
 
-    def forward(self, input_ids, cache_params=None, cache_position=None, use_cache=True, return_dict=True, attention_mask=None):
+    def forward(self, input_ids, cache_params=None, cache_position=None, use_cache=True, return_dict=True, attention_mask=None,
+                logits_to_keep=0):
         h = self.backbone.embeddings(input_ids)
         for layer in self.backbone.layers:
             h = layer(h, cache_params=cache_params, cache_position=cache_position, attention_mask=attention_mask)
+        if logits_to_keep:
+            h = h[:, -logits_to_keep:]
         return SimpleNamespace(logits=self.lm_head(self.backbone.norm_f(h)))
+
+
+def nemotron_h_8b_config():
+    """The 8B shape: 52 blocks = 24 Mamba2 + 4 attention + 24 MLP, hidden 4096, vocab 131072, FFN 21504,
+    32 query / 8 kv heads of 128, Mamba2 with 128 heads of 64, state 128, 8 groups, conv kernel 4."""
+    return SimpleNamespace(
+        hybrid_override_pattern="M-M-M-M*-M-M-M-M-M*-M-M-M-M-M*-M-M-M-M-M*-M-M-M-M-M-", hidden_size=4096, vocab_size=131072,
+        intermediate_size=21504, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+        mamba_num_heads=128, mamba_head_dim=64, mamba_intermediate=8192, ssm_state_size=128, n_groups=8, conv_kernel=4)
 
 
 def tiny_config(pattern="M-M*-M-*M", hidden=256):
