@@ -82,11 +82,9 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x, gate=None):
-        x = x.float()
         if gate is not None:
-            x = x * F.silu(gate.float())
-        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (x * self.weight.float()).to(self.weight.dtype)
+            x = x * F.silu(gate)
+        return F.rms_norm(x.to(self.weight.dtype), (self.weight.shape[0],), self.weight, self.eps)
 
 
 class Mamba2Mixer(nn.Module):
@@ -159,8 +157,17 @@ class Attention(nn.Module):
             if pk is not None:
                 k, v = torch.cat([pk, k], dim=2), torch.cat([pv, v], dim=2)
             past_key_value.key_cache[self.layer_idx], past_key_value.value_cache[self.layer_idx] = k, v
-        out = F.scaled_dot_product_attention(q, repeat_kv(k, self.num_key_value_groups), repeat_kv(v, self.num_key_value_groups),
-                                             is_causal=t > 1)
+        if t == 1:
+            # one query token: grouped matmuls with an fp32 softmax (torch's fused attention costs tens of
+            # milliseconds of host time per call for this shape on some builds)
+            g = self.num_key_value_groups
+            qg = q.reshape(b, self.num_key_value_heads, g, self.head_dim)
+            scores = torch.einsum("bkgd,bktd->bkgt", qg, k).float() * (self.head_dim ** -0.5)
+            probs = torch.softmax(scores, dim=-1).to(v.dtype)
+            out = torch.einsum("bkgt,bktd->bkgd", probs, v).reshape(b, self.num_heads, 1, self.head_dim)
+        else:
+            out = F.scaled_dot_product_attention(q, repeat_kv(k, self.num_key_value_groups), repeat_kv(v, self.num_key_value_groups),
+                                                 is_causal=True)
         return self.o_proj(out.transpose(1, 2).reshape(b, t, -1)), None, past_key_value
 
 
@@ -171,7 +178,7 @@ class MLP(nn.Module):
         self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
 
     def forward(self, x):
-        return self.down_proj(F.relu(self.up_proj(x)) ** 2)
+        return self.down_proj(F.relu(self.up_proj(x)).square())
 
 
 class Block(nn.Module):
