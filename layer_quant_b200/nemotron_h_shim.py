@@ -119,7 +119,7 @@ class Mamba2Mixer(nn.Module):
             conv_state[:, :, -1] = xbc
             xbc = F.silu((conv_state.float() * self.conv1d.weight.squeeze(1).float()).sum(-1) + self.conv1d.bias.float()).to(hs.dtype)
         x, B, C = xbc.split([self.intermediate_size, self.n_groups * self.ssm_state_size, self.n_groups * self.ssm_state_size], dim=-1)
-        A = -torch.exp(self.A_log.float())[:, None, None].expand(-1, self.head_dim, self.ssm_state_size)
+        A = (-torch.exp(self.A_log.float()))[:, None, None].expand(-1, self.head_dim, self.ssm_state_size)  # stride-0 view
         y = module.selective_state_update(  # looked up at call time: this is the symbol the MX patch replaces
             cache_params.ssm_states[self.layer_idx], x.reshape(batch, self.num_heads, self.head_dim),
             dt[:, :, None].expand(-1, -1, self.head_dim), A, B.view(batch, self.n_groups, -1), C.view(batch, self.n_groups, -1),
