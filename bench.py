@@ -37,8 +37,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 # stdout carries exactly one JSON line: keep NCCL's version / info banner off it
-if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
-    os.environ["NCCL_DEBUG"] = "WARN"
+if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO", "TRACE"):
+    os.environ["NCCL_DEBUG"] = "WARN"  # also when unset: a system-wide nccl.conf may ask for the banner
 
 HEADS, DIM, DSTATE, GROUPS, LAYERS = 128, 64, 128, 8, 24
 MX8_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 18 * 2  # 2,359,296
