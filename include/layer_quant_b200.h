@@ -205,6 +205,24 @@ size_t lq_int4_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t kv
 /* The split count the library would pick for this problem on the current device (>= 1). */
 int32_t lq_int4_decode_auto_splits(int32_t batch, int32_t kv_heads, int32_t seq_len);
 
+/* Causal attention of q_len consecutive query positions over the packed cache, which already holds
+ * their own K / V rows (lq_int4_kv_append first): query i of a sequence attends rows
+ * [0, first_len + i).  This is what the reference's _int4_prefill_attention_kernel computes
+ * (int4_8b_attention.py:114-251, first_len = 1: a prompt from position 0), a kernel the reference
+ * defines but never calls; its live prefill path attends the un-quantised K / V (:693-714).
+ * first_len > 1 serves chunked prefill behind an existing context.  Group sizes 32 / 64 / 128.  */
+typedef struct lq_int4_prefill_args {
+  lq_int4_cache cache;
+  const void* q; int64_t q_stride[4];   /* [B, Hq, Tq, D]: batch, head, position, d */
+  void* out;     int64_t out_stride[4]; /* [B, Hq, Tq, D]                            */
+  int32_t dtype;        /* of q and out */
+  int32_t q_heads;
+  int32_t q_len;
+  int32_t first_len;    /* rows the first query position sees, its own included (>= 1) */
+} lq_int4_prefill_args;
+
+int lq_int4_prefill_attn(const lq_int4_prefill_args* args, void* cuda_stream);
+
 /* lq_int4_decode_attn for callers that cannot hand over scratch memory of their own: a process
  * whose memory pool has already taken all of the device memory (a cudaMalloc would fail), or a
  * latency-critical thread that must not take the device-wide lock an allocation takes.  Same
@@ -277,7 +295,7 @@ int lq_causal_conv1d_update(const lq_conv1d_update_args* args, void* cuda_stream
 
 /* sizeof of an ABI struct as the library was compiled: 0 lq_mx_state, 1 lq_rounding,
  * 2 lq_mx_update_args, 3 lq_int4_cache, 4 lq_int4_decode_args, 5 lq_dense_update_args,
- * 6 lq_conv1d_update_args; -1 otherwise. */
+ * 6 lq_conv1d_update_args, 7 lq_int4_prefill_args; -1 otherwise. */
 int lq_abi_sizeof(int which);
 const char* lq_last_error_string(void);
 /* Reads (and clears) the device-side status word of the current device: 0, or a bit set: bit 0 a

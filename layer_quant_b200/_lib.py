@@ -100,6 +100,15 @@ class Int4DecodeArgs(C.Structure):
     ]
 
 
+class Int4PrefillArgs(C.Structure):
+    _fields_ = [
+        ("cache", Int4Cache),
+        ("q", C.c_void_p), ("q_stride", C.c_int64 * 4),
+        ("out", C.c_void_p), ("out_stride", C.c_int64 * 4),
+        ("dtype", C.c_int32), ("q_heads", C.c_int32), ("q_len", C.c_int32), ("first_len", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -125,6 +134,7 @@ def lib() -> C.CDLL:
                                     C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
     l.lq_int4_decode_attn.argtypes = [C.POINTER(Int4DecodeArgs), C.c_void_p]
     l.lq_int4_decode_attn_static.argtypes = [C.POINTER(Int4DecodeArgs), C.c_void_p]
+    l.lq_int4_prefill_attn.argtypes = [C.POINTER(Int4PrefillArgs), C.c_void_p]
     l.lq_int4_static_scratch_bytes.restype = C.c_size_t
     l.lq_int4_decode_workspace_bytes.argtypes = [C.c_int32] * 5
     l.lq_int4_decode_workspace_bytes.restype = C.c_size_t
@@ -133,7 +143,8 @@ def lib() -> C.CDLL:
     l.lq_dense_state_update.argtypes = [C.POINTER(DenseUpdateArgs), C.c_void_p]
     l.lq_causal_conv1d_update.argtypes = [C.POINTER(Conv1dUpdateArgs), C.c_void_p]
     l.lq_abi_sizeof.argtypes = [C.c_int]
-    for which, struct in enumerate((MxState, Rounding, MxUpdateArgs, Int4Cache, Int4DecodeArgs, DenseUpdateArgs, Conv1dUpdateArgs)):
+    for which, struct in enumerate((MxState, Rounding, MxUpdateArgs, Int4Cache, Int4DecodeArgs, DenseUpdateArgs, Conv1dUpdateArgs,
+                                    Int4PrefillArgs)):
         if l.lq_abi_sizeof(which) != C.sizeof(struct):
             raise RuntimeError(f"{LIB_PATH}: struct {struct.__name__} is {l.lq_abi_sizeof(which)} bytes in the library, "
                                f"{C.sizeof(struct)} in the binding; rebuild the library")

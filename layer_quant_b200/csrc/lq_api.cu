@@ -36,6 +36,7 @@ LQ_EXPORT int lq_abi_sizeof(int which) {
     case 4: return (int)sizeof(lq_int4_decode_args);
     case 5: return (int)sizeof(lq_dense_update_args);
     case 6: return (int)sizeof(lq_conv1d_update_args);
+    case 7: return (int)sizeof(lq_int4_prefill_args);
     default: return -1;
   }
 }

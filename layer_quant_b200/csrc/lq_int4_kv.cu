@@ -192,6 +192,11 @@ struct DecodeParams {
   int32_t* counters;       // [B * Hkv] tickets (workspace)
   float* part_ml;          // [B * Hq * splits * 2]
   float* part_acc;         // [B * Hq * splits * 128]
+  // causal prefill over the quantised cache (tensor-pipe kernel with QB > 0 only)
+  int32_t q_len = 1;       // query positions per sequence
+  int32_t nqb = 1;         // query blocks per sequence = ceil(q_len / QB)
+  int32_t first_len = 0;   // tokens the first query position sees (its own included)
+  int64_t q_stride_t = 0, out_stride_t = 0;
 };
 
 // The lengths a launch works with.  Without a device counter they are the host's; with one the
@@ -806,6 +811,94 @@ LQ_EXPORT int lq_int4_decode_attn(const lq_int4_decode_args* args, void* cuda_st
     case 8: return launch_decode_gs<8>(p, st);
     default:
       return fail(LQ_ERR_UNSUPPORTED, "lq_int4_decode_attn: %d query heads per kv head (supported: 1, 2, 4, 8)", a.q_heads / c.kv_heads);
+  }
+}
+
+// ---- causal prefill over the quantised cache ---------------------------------------------------------
+template <int R, int GS>
+static int launch_prefill_mma(const DecodeParams& p, cudaStream_t st) {
+  using L = mma::TileLayout<GS>;
+  constexpr int QB = 8 / R;  // query positions per CTA: R * QB = 8 head columns
+  const size_t smem = mma::kStagesM * L::kStage + L::kNewBytes;
+  const dim3 grid(static_cast<unsigned>(p.a.cache.batch) * p.nqb, p.a.cache.kv_heads, 1), block(mma::kThreadsM);
+#define LQ_PREFILL_LAUNCH(SPLIT_)                                                                                   \
+  do {                                                                                                              \
+    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, false, SPLIT_, QB>,                       \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                    \
+    mma::int4_decode_mma_kernel<R, GS, false, SPLIT_, QB><<<grid, block, smem, st>>>(p);                            \
+  } while (0)
+  if (p.a.dtype != LQ_BF16) LQ_PREFILL_LAUNCH(true); else LQ_PREFILL_LAUNCH(false);
+#undef LQ_PREFILL_LAUNCH
+  LQ_CHECK_CUDA(cudaGetLastError());
+  return LQ_OK;
+}
+
+template <int R>
+static int launch_prefill_gs(const DecodeParams& p, cudaStream_t st) {
+  switch (p.a.cache.group_size) {
+    case 32: return launch_prefill_mma<R, 32>(p, st);
+    case 64: return launch_prefill_mma<R, 64>(p, st);
+    case 128: return launch_prefill_mma<R, 128>(p, st);
+    default:
+      return fail(LQ_ERR_UNSUPPORTED, "lq_int4_prefill_attn: group_size=%d (supported: 32, 64, 128)", p.a.cache.group_size);
+  }
+}
+
+LQ_EXPORT int lq_int4_prefill_attn(const lq_int4_prefill_args* args, void* cuda_stream) {
+  LQ_CHECK_ARG(args != nullptr, "lq_int4_prefill_attn: null args");
+  const lq_int4_prefill_args& a = *args;
+  const lq_int4_cache& c = a.cache;
+  if (int rc = validate_cache(c, "lq_int4_prefill_attn")) return rc;
+  LQ_CHECK_ARG(a.q && a.out, "lq_int4_prefill_attn: null q/out");
+  LQ_CHECK_ARG(valid_dtype(a.dtype), "lq_int4_prefill_attn: bad dtype");
+  LQ_CHECK_ARG(a.q_len >= 1 && a.first_len >= 1 && static_cast<int64_t>(a.first_len) + a.q_len - 1 <= c.capacity,
+               "lq_int4_prefill_attn: first_len=%d, q_len=%d outside the cache (capacity %d)", a.first_len, a.q_len, c.capacity);
+  LQ_CHECK_ARG(a.q_heads > 0 && a.q_heads % c.kv_heads == 0, "lq_int4_prefill_attn: q_heads=%d not a multiple of kv_heads=%d",
+               a.q_heads, c.kv_heads);
+  if (c.head_dim != kHeadDim) return fail(LQ_ERR_UNSUPPORTED, "lq_int4_prefill_attn: head_dim=%d (supported: 128)", c.head_dim);
+  const int G = c.head_dim / c.group_size;
+  LQ_CHECK_ARG(c.kp_stride[3] == 1 && c.vp_stride[3] == 1 && c.kp_stride[2] == c.head_dim / 2 && c.vp_stride[2] == c.head_dim / 2,
+               "lq_int4_prefill_attn: packed K/V rows must be contiguous (token stride %d, byte stride 1)", c.head_dim / 2);
+  LQ_CHECK_ARG(c.ks_stride[3] == 1 && c.vs_stride[3] == 1 && c.ks_stride[2] == G && c.vs_stride[2] == G,
+               "lq_int4_prefill_attn: scale rows must be contiguous (token stride %d)", G);
+  LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(c.k_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(c.v_packed) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(c.k_scale) % 16 == 0 && reinterpret_cast<uintptr_t>(c.v_scale) % 16 == 0,
+               "lq_int4_prefill_attn: cache tensors must be 16-byte aligned");
+  LQ_CHECK_ARG(c.kp_stride[0] % 16 == 0 && c.kp_stride[1] % 16 == 0 && c.vp_stride[0] % 16 == 0 && c.vp_stride[1] % 16 == 0,
+               "lq_int4_prefill_attn: packed batch/head strides must be multiples of 16 bytes");
+  LQ_CHECK_ARG(c.ks_stride[0] % 4 == 0 && c.ks_stride[1] % 4 == 0 && c.vs_stride[0] % 4 == 0 && c.vs_stride[1] % 4 == 0,
+               "lq_int4_prefill_attn: scale batch/head strides must be multiples of 4 elements");
+  const int ratio = a.q_heads / c.kv_heads;
+  if (ratio != 1 && ratio != 2 && ratio != 4 && ratio != 8)
+    return fail(LQ_ERR_UNSUPPORTED, "lq_int4_prefill_attn: %d query heads per kv head (supported: 1, 2, 4, 8)", ratio);
+  DecodeParams p;
+  p.a = lq_int4_decode_args{};
+  p.a.cache = c;
+  p.a.q = a.q;
+  p.a.q_stride[0] = a.q_stride[0]; p.a.q_stride[1] = a.q_stride[1]; p.a.q_stride[2] = a.q_stride[3];
+  p.a.out = a.out;
+  p.a.out_stride[0] = a.out_stride[0]; p.a.out_stride[1] = a.out_stride[1]; p.a.out_stride[2] = a.out_stride[3];
+  p.a.dtype = a.dtype;
+  p.a.q_heads = a.q_heads;
+  p.a.seq_len = a.first_len + a.q_len - 1;
+  p.ctx_len = p.a.seq_len;
+  p.splits = 1;
+  p.tiles_per_split = (p.ctx_len + kTile - 1) / kTile;
+  p.counters = nullptr; p.part_ml = nullptr; p.part_acc = nullptr;
+  p.q_len = a.q_len;
+  p.first_len = a.first_len;
+  p.q_stride_t = a.q_stride[2];
+  p.out_stride_t = a.out_stride[2];
+  const int qb = 8 / ratio;
+  p.nqb = (a.q_len + qb - 1) / qb;
+  LQ_CHECK_ARG(static_cast<int64_t>(c.batch) * p.nqb <= 0x7FFFFFFFLL && c.kv_heads <= 65535,
+               "lq_int4_prefill_attn: batch * query blocks or kv_heads too large for one launch");
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  switch (ratio) {
+    case 1: return launch_prefill_gs<1>(p, st);
+    case 2: return launch_prefill_gs<2>(p, st);
+    case 4: return launch_prefill_gs<4>(p, st);
+    default: return launch_prefill_gs<8>(p, st);
   }
 }
 

@@ -146,8 +146,15 @@ struct TileLayout {
 // 64-token tile.  DecodeParams, int4_scale and int4_code come from lq_int4_kv.cu.
 // QSPLIT: the query is not bf16 (fp16 / fp32 callers): it enters the tensor pipe as bf16 hi (rows 0..7)
 // + bf16 lo (rows 8..15, otherwise idle), 16 bits of mantissa in all.
-template <int R, int GS, bool HAS_MASK, bool QSPLIT>
-__global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_decode_mma_kernel(const DecodeParams p) {
+// QB: 0 = decode (one query token per sequence).  QB >= 1 = causal prefill over the quantised cache: the CTA
+// serves QB consecutive query positions of one (batch, kv head), each (query, head) pair being one head
+// column with its own causal limit; R * QB <= 8 columns, one split, no mask, no fused append.
+template <int R, int GS, bool HAS_MASK, bool QSPLIT, int QB = 0>
+__global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSPLIT) ? 3 : 2)
+    int4_decode_mma_kernel(const DecodeParams p) {
+  constexpr bool PREFILL = QB > 0;
+  constexpr int RV = R * (PREFILL ? QB : 1);  // head columns in use
+  static_assert(RV <= 8 && !(PREFILL && HAS_MASK), "at most eight head columns; prefill takes no mask");
   using L = TileLayout<GS>;
   constexpr int G = L::kG;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -156,7 +163,9 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
 
   const lq_int4_decode_args& a = p.a;
   const lq_int4_cache& c = a.cache;
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int split = PREFILL ? 0 : blockIdx.x, kvh = blockIdx.y;
+  const int b = PREFILL ? static_cast<int>(blockIdx.x) / p.nqb : blockIdx.z;
+  const int q_first = PREFILL ? (static_cast<int>(blockIdx.x) - b * p.nqb) * QB : 0;  // first query position of the CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;  // mma fragment coordinates: row / column group
   // Head columns.  Both products put the heads on the n side (8 columns).  Up to four query heads per kv
@@ -164,15 +173,20 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
   // P * v_scale from columns 0..3 and the lo part from columns 4..7 of ONE n-tile.  Eight heads: columns
   // are heads, hi and lo parts go to two n-tiles.  In the Q^T fragments (B operand) column n = g; in the
   // accumulators a lane owns columns 2t and 2t + 1.
-  constexpr bool DUP = R <= 4;
+  constexpr bool DUP = RV <= 4;
   constexpr int NT = DUP ? 1 : 2;
   const int hrow = DUP ? (g & 3) : g;
   const bool is_lo = DUP && t >= 2;
   const uint32_t lo_mul = is_lo ? 65536u : 0u, lo_mask = is_lo ? 0xFFFF0000u : 0u;
-  const bool fused_new = a.k_new != nullptr;
+  const bool fused_new = !PREFILL && a.k_new != nullptr;
   uint8_t* newtile = smem + kStagesM * L::kStage;
 
-  const RunLengths rl = run_lengths(p);
+  RunLengths rl = run_lengths(p);
+  if (PREFILL) {  // the CTA reads up to its last query's own position
+    rl.seq_len = p.first_len + min(q_first + QB - 1, p.q_len - 1);
+    rl.ctx_len = rl.seq_len;
+    rl.tiles_per_split = (rl.ctx_len + kTileTok - 1) / kTileTok;
+  }
   const int ntiles = (rl.ctx_len + kTileTok - 1) / kTileTok;
   const int tile_begin = split * rl.tiles_per_split;
   const int tile_end = min(ntiles, tile_begin + rl.tiles_per_split);
@@ -253,8 +267,9 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
     for (int s = 0; s < 2; ++s) {
       const int d0 = 32 * i + 8 * t + 2 * s;
       float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-      if (hrow < R) {
-        const int64_t qb = b * a.q_stride[0] + (kvh * R + hrow) * a.q_stride[1];
+      if (hrow < RV && (!PREFILL || q_first + hrow / R < p.q_len)) {
+        const int64_t qb = b * a.q_stride[0] + (kvh * R + hrow % R) * a.q_stride[1] +
+                           (PREFILL ? (q_first + hrow / R) * p.q_stride_t : 0);
         q0 = load_as_float(a.q, qb + (d0 + 0) * a.q_stride[2], a.dtype);
         q1 = load_as_float(a.q, qb + (d0 + 4) * a.q_stride[2], a.dtype);
         q2 = load_as_float(a.q, qb + (d0 + 1) * a.q_stride[2], a.dtype);
@@ -326,7 +341,13 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[i][sp][nt][e] = 0.0f;
-  const int col_head0 = DUP ? ((2 * t) & 3) : 2 * t;  // head of accumulator column 2t (column 2t+1: the next head)
+  const int col_head0 = DUP ? ((2 * t) & 3) : 2 * t;  // head column of accumulator column 2t (column 2t+1: the next one)
+  // prefill: the tokens a column may see, [0, its query's position]
+  int col_limit[2] = {0x7FFFFFFF, 0x7FFFFFFF};
+  if (PREFILL) {
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) col_limit[cc] = p.first_len + min(q_first + (col_head0 + cc) / R, p.q_len - 1);
+  }
   float m_run[2] = {kNegBigM, kNegBigM}, l_run[2] = {0.0f, 0.0f};  // this lane's two columns (l: this lane's share)
 
   // Per-thread offsets inside a tile for this warp's 16 rows (row0 = 16 * warp; 0 for the new-row tile):
@@ -391,7 +412,7 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
         for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], sacc[i][2 * r + cc], sum);
         sum *= scale_sm;
         if (HAS_MASK) sum += bias;
-        sv[r][cc] = (FULL || rr < valid) ? sum : -INFINITY;
+        sv[r][cc] = ((FULL || rr < valid) && (!PREFILL || tok_first + rr < col_limit[cc])) ? sum : -INFINITY;
       }
     }
     // online softmax per column; the running max of a column is shared by the eight lanes that hold it.
@@ -523,19 +544,19 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
         }
         const int head = col_head0 + (e & 1);
         const int dim = 32 * i + 4 * g + 2 * sp + (e >> 1);
-        if ((!DUP || t < 2) && head < R) s_acc[(warp * R + head) * kD + dim] = v;
+        if ((!DUP || t < 2) && head < RV) s_acc[(warp * RV + head) * kD + dim] = v;
       }
   if (g == 0 && (!DUP || t < 2)) {
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc)
-      if (col_head0 + cc < R) {
+      if (col_head0 + cc < RV) {
         s_m[warp][col_head0 + cc] = m_run[cc];
         s_l[warp][col_head0 + cc] = l_run[cc];
       }
   }
   __syncthreads();
   const int hq0 = kvh * R;
-  for (int o = threadIdx.x; o < R * kD; o += kThreadsM) {
+  for (int o = threadIdx.x; o < RV * kD; o += kThreadsM) {
     const int r = o / kD, d = o - r * kD;
     float M = kNegBigM;
 #pragma unroll
@@ -545,9 +566,14 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
     for (int w = 0; w < kWarpsM; ++w) {
       const float fct = exp2f(s_m[w][r] - M);
       Lsum = fmaf(s_l[w][r], fct, Lsum);
-      O = fmaf(s_acc[(w * R + r) * kD + d], fct, O);
+      O = fmaf(s_acc[(w * RV + r) * kD + d], fct, O);
     }
-    if (p.splits == 1) {
+    if (PREFILL) {
+      const int qi = q_first + r / R;
+      if (qi < p.q_len)
+        store_from_float(a.out, b * a.out_stride[0] + (hq0 + r % R) * a.out_stride[1] + qi * p.out_stride_t + d * a.out_stride[2],
+                         a.dtype, O / Lsum);
+    } else if (p.splits == 1) {
       store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / Lsum);
     } else {
       const int64_t slot = (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits + split;
@@ -558,7 +584,7 @@ __global__ void __launch_bounds__(kThreadsM, (R <= 4 && !QSPLIT) ? 3 : 2) int4_d
       }
     }
   }
-  if (p.splits == 1) return;
+  if (PREFILL || p.splits == 1) return;
 
   // Ticket: the CTA that completes the set merges the splits.  No CTA waits for another.
   __threadfence();

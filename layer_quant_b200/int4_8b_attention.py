@@ -14,11 +14,13 @@ here                                           reference (int4_8b_attention.py)
 ``_decode_attention_mask``                     :569-591
 ``_forward_fused_int4_kv``                     :628-714  (decode: append fused into attention)
 ``patch_nemotron_h_attention_int4_kv``         :717-731
+``_prefill_attention``                         :114-251  (kernel the reference never calls)
 =============================================  ==========================================
 
-The cache tensors have exactly the reference's shapes, dtypes and bit layout.  The dead prefill
-kernel of the reference (``_int4_prefill_attention_kernel`` :114-251, no caller) is not mirrored:
-as in the reference, prefill attends over the un-quantised K/V with torch SDPA after packing.
+The cache tensors have exactly the reference's shapes, dtypes and bit layout.  As in the reference,
+prefill attends over the un-quantised K/V with torch SDPA after packing; the reference's unused
+``_int4_prefill_attention_kernel`` (:114-251) has its counterpart in ``_prefill_attention`` (causal
+attention over the quantised cache), used by the forward only when ``PREFILL_FROM_INT4_CACHE`` is set.
 """
 from __future__ import annotations
 
@@ -308,6 +310,36 @@ def _append_decode_attention(query_states, key_states, value_states, cache, seq_
     return out
 
 
+# When True, prefill (q_len > 1, no attention_mask) attends the quantised cache, as the reference's unused
+# prefill kernel would (:114-251), instead of the un-quantised K / V of the live path (:693-714).
+PREFILL_FROM_INT4_CACHE = False
+
+
+def _prefill_attention(query_states: torch.Tensor, cache: Int4KVLayerCache, first_len: int, num_key_value_groups: int,
+                       group_size: int, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of the q_len query positions of ``query_states`` [B, Hq, Tq, D] over cache rows that
+    already hold their K / V: position i attends rows [0, first_len + i).  Returns [B, Hq, Tq, D] in the
+    query's dtype.  ``first_len = 1`` is a prompt from position 0 (the reference's unused
+    ``_int4_prefill_attention_kernel``, :114-251); larger values continue an existing context."""
+    batch, n_heads, q_len, head_dim = query_states.shape
+    if n_heads != cache.k_packed.shape[1] * num_key_value_groups:
+        raise ValueError(f"{n_heads} query heads != {cache.k_packed.shape[1]} kv heads x {num_key_value_groups}")
+    dev = _lib.require_cuda(query_states, out)
+    if out is None:
+        out = torch.empty((batch, n_heads, q_len, head_dim), device=dev, dtype=query_states.dtype)
+    a = _lib.Int4PrefillArgs()
+    a.cache = _cache_struct(cache, group_size)
+    if a.cache.batch != batch or a.cache.head_dim != head_dim:
+        raise ValueError(f"cache [{a.cache.batch},*,*,{a.cache.head_dim}] does not match query {tuple(query_states.shape)}")
+    a.q, a.out = query_states.data_ptr(), out.data_ptr()
+    for i in range(4):
+        a.q_stride[i], a.out_stride[i] = query_states.stride(i), out.stride(i)
+    a.dtype = _lib.dtype_code(query_states)
+    a.q_heads, a.q_len, a.first_len = n_heads, q_len, first_len
+    _lib.check(_lib.lib().lq_int4_prefill_attn(ct.byref(a), _lib.stream_ptr(dev)))
+    return out
+
+
 def prepare_graph_decode(past_key_value, max_len: int) -> None:
     """Make the decode steps that follow replayable from a CUDA graph (not in the reference, which
     reads the position back on the host every step, :515 / :667): every layer cache is grown once to
@@ -389,6 +421,10 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
         return self.o_proj(attn.reshape(bsz, 1, -1)), None, past_key_value
 
     _pack_kv_into_cache(layer_cache, key_states, value_states, positions, group_size, known_len=required_len)
+    if PREFILL_FROM_INT4_CACHE and attention_mask is None and group_size in (32, 64, 128):
+        # contiguous positions ending at required_len - 1 (what _positions hands out for a prompt or a chunk)
+        attn = _prefill_attention(query_states, layer_cache, required_len - q_len + 1, self.num_key_value_groups, group_size)
+        return self.o_proj(attn.transpose(1, 2).reshape(bsz, q_len, -1)), None, past_key_value
     k_full = self._int4_kv_repeat_kv(key_states, self.num_key_value_groups)
     v_full = self._int4_kv_repeat_kv(value_states, self.num_key_value_groups)
     causal_mask = attention_mask

@@ -26,6 +26,6 @@ from .mx_codec import (  # noqa: F401
 from .mx_state import mx_state_update, reference_rng_offsets  # noqa: F401
 from .int4_kv import (  # noqa: F401
     int4_encode, int4_decode, int4_pack_nibbles, int4_unpack_nibbles, int4_quant_dequant,
-    int4_decode_attention, decode_attention_mask,
+    int4_decode_attention, decode_attention_mask, int4_prefill_attention,
 )
 from .dense_state import dense_state_update, causal_conv1d_update  # noqa: F401

@@ -97,3 +97,23 @@ def int4_decode_attention(q, k_packed, v_packed, k_scale, v_scale, seq_len: int,
     p = np.exp(s)
     p = p / p.sum(axis=-1, keepdims=True)
     return np.einsum("bht,bhtd->bhd", p, v)
+
+
+def int4_prefill_attention(q, k_packed, v_packed, k_scale, v_scale, first_len: int, group_size: int) -> np.ndarray:
+    """Causal attention of q [B,Hq,Tq,D] over the packed cache: query i sees rows [0, first_len + i)
+    (the reference's unused _int4_prefill_attention_kernel, :160-251, has first_len = 1 through
+    causal_len = q_pos + 1).  Returns float64 [B,Hq,Tq,D]."""
+    q = np.asarray(q, dtype=np.float64)
+    bsz, hq, tq, d = q.shape
+    hkv = k_packed.shape[1]
+    ratio = hq // hkv
+    total = first_len + tq - 1
+    k = np.repeat(int4_decode(int4_unpack_nibbles(k_packed[:, :, :total]), k_scale[:, :, :total], group_size).astype(np.float64), ratio, axis=1)
+    v = np.repeat(int4_decode(int4_unpack_nibbles(v_packed[:, :, :total]), v_scale[:, :, :total], group_size).astype(np.float64), ratio, axis=1)
+    s = np.einsum("bhqd,bhtd->bhqt", q, k) / np.sqrt(float(d))
+    allowed = np.arange(total)[None, :] < (first_len + np.arange(tq))[:, None]
+    s = np.where(allowed[None, None], s, -np.inf)
+    s = s - s.max(axis=-1, keepdims=True)
+    p = np.exp(s)
+    p = p / p.sum(axis=-1, keepdims=True)
+    return np.einsum("bhqt,bhtd->bhqd", p, v)

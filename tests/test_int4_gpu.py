@@ -339,3 +339,32 @@ def test_recorded_launch_follows_device_length(gs, dtype):
     plan.launch()
     assert _lib.device_status() & 2
     assert _lib.device_status() == 0  # reading clears it
+
+
+@pytest.mark.parametrize("gs,ratio,tq,first", [(32, 4, 37, 1), (32, 4, 130, 1), (64, 4, 19, 100), (128, 2, 21, 1), (32, 1, 23, 7),
+                                                (64, 8, 9, 60), (32, 4, 1, 300)])
+def test_prefill_over_the_quantised_cache(gs, ratio, tq, first):
+    """Causal attention of a block of query positions over cache rows that already hold their K / V: every
+    position must equal the oracle and the decode kernel run on that position alone."""
+    m = ia()
+    b, hkv = 2, 2
+    hq = hkv * ratio
+    total = first + tq - 1
+    k, v = make_kv(31 + tq, b, hkv, total)
+    q = bf16r(np.random.default_rng(tq).standard_normal((b, hq, tq, 128)))
+    cache = fill_cache(m, k, v, gs, capacity=(total + 5 + 15) // 16 * 16)  # scale rows of a head stay 16-byte aligned
+    ref = oracle.int4_prefill_attention(q, *cache_np(cache), first, gs)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = m._prefill_attention(t(q, dtype), cache, first, ratio, gs)
+        assert tuple(out.shape) == (b, hq, tq, 128) and out.dtype == dtype
+        assert_out_close(out, ref)
+    # the same through a strided query view ([B, Tq, Hq, D] storage, as the projections leave it)
+    qs = t(np.ascontiguousarray(q.transpose(0, 2, 1, 3)), torch.bfloat16).transpose(1, 2)
+    assert_out_close(m._prefill_attention(qs, cache, first, ratio, gs), ref)
+    for i in (0, tq // 2, tq - 1):
+        one = m._decode_attention(t(q[:, :, i:i + 1], torch.float32), cache, first + i, ratio, gs)
+        assert_out_close(one, ref[:, :, i])
+    with pytest.raises(ValueError):
+        m._prefill_attention(t(q, torch.bfloat16), cache, cache.k_packed.shape[2] + 1, ratio, gs)  # runs past the capacity
+    from layer_quant_b200 import _lib
+    assert _lib.device_status() == 0

@@ -211,3 +211,27 @@ def test_whole_decode_step_replays_from_a_cuda_graph():
     finally:
         shim.selective_state_update = original_ssu
         shim._mamba_decode_state_kernel_caches = {}
+
+
+def test_prefill_from_the_quantised_cache_in_the_forward():
+    """With PREFILL_FROM_INT4_CACHE the attention forward serves a prompt from the packed cache; the prompt's
+    last-position logits must track the default path (SDPA over the un-quantised K / V) closely: the only
+    difference is INT4 rounding of K / V inside the prompt."""
+    from layer_quant_b200 import int4_8b_attention as ia
+    model, cfg = _model(seed=5)
+    ia.patch_nemotron_h_attention_int4_kv(model, group_size=32)
+    ids = torch.randint(0, cfg.vocab_size, (BATCH, CTX), generator=torch.Generator().manual_seed(6)).cuda()
+    outs = []
+    try:
+        for flag in (False, True):
+            ia.PREFILL_FROM_INT4_CACHE = flag
+            cache = shim.HybridMambaAttentionDynamicCache(cfg, BATCH, torch.bfloat16, device=ids.device)
+            with torch.inference_mode():
+                outs.append(model(ids, cache_params=cache, cache_position=torch.arange(CTX, device=ids.device)).logits.float())
+            assert all(c.length == CTX for c in ia._cache_dict(cache).values())
+    finally:
+        ia.PREFILL_FROM_INT4_CACHE = False
+    assert not torch.equal(outs[0], outs[1])
+    assert _kl(outs[0][:, -1:], outs[1][:, -1:]) < 5e-3
+    scale = float(outs[0].abs().max())
+    assert float((outs[0] - outs[1]).abs().max()) < 0.1 * scale
