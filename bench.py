@@ -554,12 +554,27 @@ def main() -> int:
                                                   "us_per_launch": round(s / (5 * reps) * 1e6, 1)}
             del caches
             torch.cuda.empty_cache()
+        # prefill over the quantised cache (the step before decode): a 1024-token prompt, 8 sequences, one layer,
+        # beside torch's fused attention over the un-quantised bf16 K / V (what the forward uses by default)
+        import torch.nn.functional as F
+        bb, tq = 8, 1024
+        c = ia._allocate_layer_cache(bb, 8, tq, 128, 4, dev)
+        kk, vv = randn(bb, 8, tq, 128), randn(bb, 8, tq, 128)
+        ia._pack_kv_into_cache(c, kk, vv, torch.arange(tq, device=dev), 32)
+        qq = randn(bb, 32, tq, 128)
+        pre_out = torch.empty_like(qq)
+        s = timed(lambda: ia._prefill_attention(qq, c, 1, 4, 32, out=pre_out), 5, 3)
+        kf, vf = kk.repeat_interleave(4, dim=1), vv.repeat_interleave(4, dim=1)
+        s2 = timed(lambda: F.scaled_dot_product_attention(qq, kf, vf, is_causal=True), 5, 3)
+        sweep["int4_prefill_b8_q1024"] = {"us_per_launch": round(s / 5 * 1e6, 1), "torch_sdpa_bf16_us": round(s2 / 5 * 1e6, 1),
+                                          "cache_bytes_read": int(bb * 8 * 160 * sum(min(i + 2, tq) for i in range(0, tq, 2)))}
+        del c, kk, vv, qq, kf, vf, pre_out
+        torch.cuda.empty_cache()
         if rank == 0 and not args.no_cpu_baseline:
             # BASELINE config 0 on the host cores, the reference's own CPU-runnable path: torch fake-quant of K / V
             # (int4_quant_dequant, group 32) + scaled_dot_product_attention, batch 1, 1024 tokens; beside it the
             # (1, 1024) cell above is the same problem on the GPU.
             import time
-            import torch.nn.functional as F
             gq = torch.Generator().manual_seed(0)
             q0 = torch.randn(1, 32, 1, 128, generator=gq).to(torch.bfloat16)
             k0, v0 = (torch.randn(1, 8, 1024, 128, generator=gq).to(torch.bfloat16) for _ in range(2))
