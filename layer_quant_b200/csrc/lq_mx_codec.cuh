@@ -115,15 +115,25 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
     const float micf = set_gt(pa[j], thresh);
     const float inv = fmaf(micf, neg_half_inv0, inv0);  // 1 / (base * 2^micro), exact
     macc = fmaf(micf, static_cast<float>(1 << j), macc);
+    if (kFixed) {  // the pair shares 1 / scale: one packed fp32x2 FMA for both values
+      float cf[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = 2 * j + k;
+        const uint32_t c = (MODE == LQ_ROUND_SUPPLIED_FIXED) ? (0x47400000u | (rnd[i] & 0xFFu))
+                                                             : __byte_perm(pw[i >> 2], 0x47400000u, 0x7650 + (i & 3));
+        cf[k] = __uint_as_float(c);
+      }
+      const float2 t2 = __ffma2_rn(make_float2(h[2 * j], h[2 * j + 1]), make_float2(inv, inv), make_float2(cf[0], cf[1]));
+      tb[2 * j] = __float_as_uint(t2.x);
+      tb[2 * j + 1] = __float_as_uint(t2.y);
+      continue;
+    }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const int i = 2 * j + k;
       float t;
-      if (kFixed) {
-        const uint32_t c = (MODE == LQ_ROUND_SUPPLIED_FIXED) ? (0x47400000u | (rnd[i] & 0xFFu))
-                                                             : __byte_perm(pw[i >> 2], 0x47400000u, 0x7650 + (i & 3));
-        t = fmaf(h[i], inv, __uint_as_float(c));
-      } else {
+      {
         const float a = fminf(fabsf(h[i]) * inv, M);
         float lvl;
         if (MODE == LQ_ROUND_HALF_UP) {
@@ -152,6 +162,27 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
   micro_bits = __float_as_uint(macc + 8388608.0f) & 0xFFu;
 }
 
+// h' = h * dA + B * dtx on 16 values and the block's share of <h', C>, with packed fp32x2 instructions
+// (sm_100: two IEEE fp32 results per instruction, same rounding per component as the scalar forms).
+// Association as everywhere in this library: t = B * dtx rounded, then fma(h, dA, t); the read-out keeps
+// four partial sums over i mod 4, added as (y0 + y1) + (y2 + y3).
+__device__ __forceinline__ float mx_update_readout16(float (&hv)[16], const float (&Bv)[16], const float (&Cv)[16], float dA,
+                                                     float dtx) {
+  const float2 dA2 = make_float2(dA, dA), dtx2 = make_float2(dtx, dtx);
+  float2 ya = make_float2(0.0f, 0.0f), yb = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float2 t0 = __fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dtx2);
+    const float2 t1 = __fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dtx2);
+    const float2 h0 = __ffma2_rn(make_float2(hv[i], hv[i + 1]), dA2, t0);
+    const float2 h1 = __ffma2_rn(make_float2(hv[i + 2], hv[i + 3]), dA2, t1);
+    hv[i] = h0.x; hv[i + 1] = h0.y; hv[i + 2] = h1.x; hv[i + 3] = h1.y;
+    ya = __ffma2_rn(h0, make_float2(Cv[i], Cv[i + 1]), ya);
+    yb = __ffma2_rn(h1, make_float2(Cv[i + 2], Cv[i + 3]), yb);
+  }
+  return (ya.x + ya.y) + (yb.x + yb.y);
+}
+
 // int8 lanes of `codes` times 2^(e - 127 + micro of the pair) -> fp32 (reference :132).
 // Fast path (stored exponent in [1, 229], everything the codec itself writes is in [28, 252] and
 // states of realistic magnitude stay far below 229): byte -> float by one byte-permute into the
@@ -164,13 +195,17 @@ __device__ __forceinline__ void mx_decode_block(const uint32_t (&codes)[4], uint
     for (int j = 0; j < 8; ++j) {
       const float s = __uint_as_float((micro_bits & (1u << j)) * (1u << (23 - j)) + ebits);
       const float cs = -32896.0f * s;
+      float f[2];
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int i = 2 * j + k;
         const uint32_t biased = codes[i >> 2] ^ 0x80808080u;  // q + 128 as unsigned bytes
-        const float f = __uint_as_float(__byte_perm(biased, 0x47000000u, 0x7604 | ((i & 3) << 4)));  // 32768 + 128 + q
-        h[i] = fmaf(f, s, cs);
+        f[k] = __uint_as_float(__byte_perm(biased, 0x47000000u, 0x7604 | ((i & 3) << 4)));  // 32768 + 128 + q
       }
+      // the pair shares its scale: one packed fp32x2 FMA (sm_100) instead of two scalar ones
+      const float2 r = __ffma2_rn(make_float2(f[0], f[1]), make_float2(s, s), make_float2(cs, cs));
+      h[2 * j] = r.x;
+      h[2 * j + 1] = r.y;
     }
   } else {  // exponents no quantiser emits: plain, overflow-safe form
     const float s0 = mx_decode_scale(e, 0), s1 = mx_decode_scale(e, 1);

@@ -254,34 +254,29 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
         mx_decode_block(codes, cur.e, cur.mic, hv);
         const float xv = sxh[p];
         if (hoisted) {
-          const float dtx = dt_h * xv;  // h' = h exp(A dt) + B (dt x)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
+          y = mx_update_readout16(hv, Bv, Cv, dA_h, dt_h * xv);  // h' = h exp(A dt) + B (dt x)
         } else {
           const float dt = d.dt_uniform ? dt_h : row_dt(h, p);
           const float dtx = dt * xv;
           if (d.a_scalar) {
-            const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + Bv[i] * dtx;
+            y = mx_update_readout16(hv, Bv, Cv, expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt), dtx);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
-              hv[i] = hv[i] * expf(Ai * dt) + Bv[i] * dtx;
+              hv[i] = fmaf(hv[i], expf(Ai * dt), Bv[i] * dtx);
             }
+            float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              y0 = fmaf(hv[i], Cv[i], y0);
+              y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
+              y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
+              y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
+            }
+            y = (y0 + y1) + (y2 + y3);
           }
         }
-        float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          y0 = fmaf(hv[i], Cv[i], y0);
-          y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
-          y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
-          y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
-        }
-        y = (y0 + y1) + (y2 + y3);
-
         const uint64_t lin = lin_head + static_cast<uint64_t>(static_cast<uint32_t>(p) * static_cast<uint32_t>(N));
         if (a.h_out) {
           float4* dst = reinterpret_cast<float4*>(a.h_out + lin);
@@ -429,17 +424,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
       float hv[16];
       mx_decode_block(codes, cur.e, cur.mic, hv);
       const float dtx = dt_h * sx[row];  // h' = h exp(A dt) + B (dt x)
-#pragma unroll
-      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
-      float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 16; i += 4) {
-        y0 = fmaf(hv[i], Cv[i], y0);
-        y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
-        y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
-        y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
-      }
-      float y = (y0 + y1) + (y2 + y3);
+      float y = mx_update_readout16(hv, Bv, Cv, dA_h, dtx);
 
       const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
       uint32_t e_new, mic_new;
