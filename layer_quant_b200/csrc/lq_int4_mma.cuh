@@ -405,12 +405,18 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
         const int n = tok_first + rr;
         bias = ((FULL || rr < valid) && n < a.mask_k_len) ? a.mask[b * a.mask_stride_b + n * a.mask_stride_k] : -INFINITY;
       }
+      // both columns of the token at once: packed fp32x2 FMA / MUL (sm_100), same rounding per component
+      float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float k = sc[(32 * i) / GS];
+        sum2 = __ffma2_rn(make_float2(k, k), make_float2(sacc[i][2 * r], sacc[i][2 * r + 1]), sum2);
+      }
+      sum2 = __fmul2_rn(sum2, make_float2(scale_sm, scale_sm));
+      const float sums[2] = {sum2.x, sum2.y};
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sum = fmaf(sc[(32 * i) / GS], sacc[i][2 * r + cc], sum);
-        sum *= scale_sm;
+        float sum = sums[cc];
         if (HAS_MASK) sum += bias;
         sv[r][cc] = ((FULL || rr < valid) && (!PREFILL || tok_first + rr < col_limit[cc])) ? sum : -INFINITY;
       }
@@ -463,14 +469,15 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
       load_scales(vsc + so[r], vs);
 #pragma unroll
       for (int q = 0; q < G; ++q) {
-        const float p0 = pv[r][0] * vs[q], p1 = pv[r][1] * vs[q];
-        const uint32_t hi = pack_bf16x2(p0, p1);
+        const float2 pp = __fmul2_rn(make_float2(pv[r][0], pv[r][1]), make_float2(vs[q], vs[q]));
+        const uint32_t hi = pack_bf16x2(pp.x, pp.y);
         if (DUP) {
-          pb[q][r][0] = movmatrix_trans(pack_bf16x2(p0 - __uint_as_float(hi * lo_mul), p1 - __uint_as_float(hi & lo_mask)));
+          const float2 lo = __ffma2_rn(make_float2(__uint_as_float(hi * lo_mul), __uint_as_float(hi & lo_mask)), make_float2(-1.0f, -1.0f), pp);
+          pb[q][r][0] = movmatrix_trans(pack_bf16x2(lo.x, lo.y));
         } else {
+          const float2 lo = __ffma2_rn(make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xFFFF0000u)), make_float2(-1.0f, -1.0f), pp);
           pb[q][r][0] = movmatrix_trans(hi);
-          pb[q][r][NT - 1] =
-              movmatrix_trans(pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xFFFF0000u)));
+          pb[q][r][NT - 1] = movmatrix_trans(pack_bf16x2(lo.x, lo.y));
         }
       }
     }
