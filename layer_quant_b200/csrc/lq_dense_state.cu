@@ -102,6 +102,22 @@ __device__ __forceinline__ void dense_store16(void* base, int64_t off, bool vec,
   }
 }
 
+// h' = h * dA + B * dtx on 16 values and their share of <h', C>, two values per packed fp32x2 instruction (sm_100)
+__device__ __forceinline__ float dense_update_readout16(float (&hv)[16], const float (&Bv)[16], const float (&Cv)[16], float dA,
+                                                        float dtx) {
+  const float2 dA2 = make_float2(dA, dA), dtx2 = make_float2(dtx, dtx);
+  float2 ya = make_float2(0.0f, 0.0f), yb = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float2 h0 = __ffma2_rn(make_float2(hv[i], hv[i + 1]), dA2, __fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dtx2));
+    const float2 h1 = __ffma2_rn(make_float2(hv[i + 2], hv[i + 3]), dA2, __fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dtx2));
+    hv[i] = h0.x; hv[i + 1] = h0.y; hv[i + 2] = h1.x; hv[i + 3] = h1.y;
+    ya = __ffma2_rn(h0, make_float2(Cv[i], Cv[i + 1]), ya);
+    yb = __ffma2_rn(h1, make_float2(Cv[i + 2], Cv[i + 3]), yb);
+  }
+  return (ya.x + ya.y) + (yb.x + yb.y);
+}
+
 // h' = h exp(A dt) + B (dt x) on one 16-value block, and the block's share of <h', C>
 struct DenseRowCtx {
   const lq_dense_update_args* a;
@@ -385,18 +401,7 @@ __global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_ring_kern
     const int srow = chh * P + crow;
     if (active) {
       if (SIMPLE) {
-        const float dtx = dt_h * sx[srow];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
-        float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          y0 = fmaf(hv[i], Cv[i], y0);
-          y1 = fmaf(hv[i + 1], Cv[i + 1], y1);
-          y2 = fmaf(hv[i + 2], Cv[i + 2], y2);
-          y3 = fmaf(hv[i + 3], Cv[i + 3], y3);
-        }
-        y = (y0 + y1) + (y2 + y3);
+        y = dense_update_readout16(hv, Bv, Cv, dA_h, dt_h * sx[srow]);
       } else {
         y = dense_row_update(rc, hv, Bv, Cv, h0 + chh, crow, sx[srow], dt_h, dA_h);
       }
