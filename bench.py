@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Headline workload (BASELINE config 1, the configuration the metric is quoted on): the fused Mamba2
+Headline workload (benchmark configuration 1, the configuration the metric is quoted on): the fused Mamba2
 MX8 state update at batch 8 per GPU, 128 heads x 64 x 128 state, 8 B/C groups, stochastic
 rounding, for the 24 Mamba2 layers of one Nemotron-H-8B decode step.  One "step" = those 24
 per-layer launches over 24 distinct layer states (453 MB of packed state per step, larger than
@@ -142,7 +142,7 @@ def reference_arm(args, rank: int, world: int) -> int:
 
 def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> dict:
     return {
-        "workload": "BASELINE config 1: Mamba2 MX8 state update, one Nemotron-H-8B decode step = 24 layers",
+        "workload": "benchmark configuration 1: Mamba2 MX8 state update, one Nemotron-H-8B decode step = 24 layers",
         "batch_per_gpu": batch_per_gpu, "global_batch": batch_per_gpu * n_gpus, "heads": HEADS, "head_dim": DIM, "d_state": DSTATE,
         "bc_groups": GROUPS, "layers_per_step": LAYERS, "state_format": "MX8 packed (18 B / 16-value block)",
         "rounding": f"stochastic, Philox4x32-10, {rng} stream, seed 0", "parallelism": f"batch-sharded dp{n_gpus}, no collective",
@@ -151,7 +151,7 @@ def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> 
 
 
 def model_case(args, dev, rank, world):
-    """BASELINE config 4 in this repository's terms: a random-init Nemotron-H-8B-shaped model
+    """benchmark configuration 4 in this repository's terms: a random-init Nemotron-H-8B-shaped model
     (layer_quant_b200/nemotron_h_shim.py; projections, norms and MLP are torch library calls) decodes
     ``--model-steps`` teacher-forced random tokens after a ``--model-prompt``-token prompt, first unpatched (bf16 KV
     cache, bf16 SSM state through the library's dense-state kernel), then with INT4 KV (group 32) + MX8 state on every
@@ -571,7 +571,7 @@ def main() -> int:
         del c, kk, vv, qq, kf, vf, pre_out
         torch.cuda.empty_cache()
         if rank == 0 and not args.no_cpu_baseline:
-            # BASELINE config 0 on the host cores, the reference's own CPU-runnable path: torch fake-quant of K / V
+            # benchmark configuration 0 on the host cores, the reference's own CPU-runnable path: torch fake-quant of K / V
             # (int4_quant_dequant, group 32) + scaled_dot_product_attention, batch 1, 1024 tokens; beside it the
             # (1, 1024) cell above is the same problem on the GPU.
             import time

@@ -18,7 +18,7 @@ MX4_STATE_BYTES_PER_SEQ_LAYER = 8192 * 8 * 10 * 2
 
 
 def make_config1_inputs(batch: int, seed: int = 0, heads: int = 128, dim: int = 64, dstate: int = 128, groups: int = 8):
-    """BASELINE config 1 operands (numpy fp32 holding bf16-representable values where the model
+    """benchmark configuration 1 operands (numpy fp32 holding bf16-representable values where the model
     uses bf16): state ~ N(0, 0.5), x, B, C ~ N(0, 1), dt ~ N(0, 1) per head, dt_bias ~ U(-4, -2),
     A = -exp(U(0, ln 16)), D ~ U(0, 1)."""
     rng = np.random.default_rng(seed)

@@ -120,7 +120,7 @@ def test_decode_context_lengths_and_splits(tlen):
 
 
 def test_config0_shape_against_reference_cpu_path():
-    """BASELINE config 0: batch 1, 32 query / 8 kv heads, head_dim 128, context 1024, group 32, bf16
+    """benchmark configuration 0: batch 1, 32 query / 8 kv heads, head_dim 128, context 1024, group 32, bf16
     N(0,1) from seed 0.  Compared with the reference's PyTorch path (fake-quantised K/V + softmax
     attention) evaluated in float64."""
     m = ia()

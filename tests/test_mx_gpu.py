@@ -159,7 +159,7 @@ def test_fused_update_against_reference_fixtures(path, layout):
 
 @pytest.mark.parametrize("bits,layout", [(8, "packed"), (8, "reference"), (4, "packed"), (4, "reference")])
 def test_fused_update_config1_shape_against_oracle(bits, layout):
-    """BASELINE config 1 (B=8, H=128, P=64, N=128, G=8; MX8) and its MX4 variant, two steps,
+    """benchmark configuration 1 (B=8, H=128, P=64, N=128, G=8; MX8) and its MX4 variant, two steps,
     reference Philox stream with seed 0."""
     m = mk()
     mmax = 63 if bits == 8 else 7
