@@ -889,7 +889,7 @@ LQ_EXPORT int lq_int4_prefill_attn(const lq_int4_prefill_args* args, void* cuda_
   p.first_len = a.first_len;
   p.q_stride_t = a.q_stride[2];
   p.out_stride_t = a.out_stride[2];
-  const int qb = 8 / ratio;
+  const int qb = (8 / ratio) * mma::kWarpsM;  // query positions per CTA: 8 / ratio per warp
   p.nqb = (a.q_len + qb - 1) / qb;
   LQ_CHECK_ARG(static_cast<int64_t>(c.batch) * p.nqb <= 0x7FFFFFFFLL && c.kv_heads <= 65535,
                "lq_int4_prefill_attn: batch * query blocks or kv_heads too large for one launch");

@@ -146,9 +146,11 @@ struct TileLayout {
 // 64-token tile.  DecodeParams, int4_scale and int4_code come from lq_int4_kv.cu.
 // QSPLIT: the query is not bf16 (fp16 / fp32 callers): it enters the tensor pipe as bf16 hi (rows 0..7)
 // + bf16 lo (rows 8..15, otherwise idle), 16 bits of mantissa in all.
-// QB: 0 = decode (one query token per sequence).  QB >= 1 = causal prefill over the quantised cache: the CTA
-// serves QB consecutive query positions of one (batch, kv head), each (query, head) pair being one head
-// column with its own causal limit; R * QB <= 8 columns, one split, no mask, no fused append.
+// QB: 0 = decode (one query token per sequence).  QB >= 1 = causal prefill over the quantised cache: every
+// WARP of the CTA serves QB consecutive query positions of one (batch, kv head) -- 4 QB positions per CTA --
+// each (query, head) pair being one head column with its own causal limit (R * QB <= 8 columns); a warp
+// walks all 64 tokens of every staged tile its positions may see, so a tile is fetched once for 4 QB
+// positions and nothing is merged between warps.  One split, no mask, no fused append.
 template <int R, int GS, bool HAS_MASK, bool QSPLIT, int QB = 0>
 __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSPLIT) ? 3 : 2)
     int4_decode_mma_kernel(const DecodeParams p) {
@@ -165,9 +167,10 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
   const lq_int4_cache& c = a.cache;
   const int split = PREFILL ? 0 : blockIdx.x, kvh = blockIdx.y;
   const int b = PREFILL ? static_cast<int>(blockIdx.x) / p.nqb : blockIdx.z;
-  const int q_first = PREFILL ? (static_cast<int>(blockIdx.x) - b * p.nqb) * QB : 0;  // first query position of the CTA
+  const int cta_q_first = PREFILL ? (static_cast<int>(blockIdx.x) - b * p.nqb) * (QB * kWarpsM) : 0;  // first position of the CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;  // mma fragment coordinates: row / column group
+  const int q_first = PREFILL ? cta_q_first + warp * QB : 0;  // first query position of this warp
   // Head columns.  Both products put the heads on the n side (8 columns).  Up to four query heads per kv
   // head: columns 4..7 repeat columns 0..3, so that the O^T product can take the bf16 hi part of
   // P * v_scale from columns 0..3 and the lo part from columns 4..7 of ONE n-tile.  Eight heads: columns
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
 
   RunLengths rl = run_lengths(p);
   if (PREFILL) {  // the CTA reads up to its last query's own position
-    rl.seq_len = p.first_len + min(q_first + QB - 1, p.q_len - 1);
+    rl.seq_len = p.first_len + min(cta_q_first + QB * kWarpsM - 1, p.q_len - 1);
     rl.ctx_len = rl.seq_len;
     rl.tiles_per_split = (rl.ctx_len + kTileTok - 1) / kTileTok;
   }
@@ -344,9 +347,11 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
   const int col_head0 = DUP ? ((2 * t) & 3) : 2 * t;  // head column of accumulator column 2t (column 2t+1: the next one)
   // prefill: the tokens a column may see, [0, its query's position]
   int col_limit[2] = {0x7FFFFFFF, 0x7FFFFFFF};
+  int warp_limit = 0x7FFFFFFF;  // tokens this warp's positions may see at all (0: the warp has no position)
   if (PREFILL) {
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) col_limit[cc] = p.first_len + min(q_first + (col_head0 + cc) / R, p.q_len - 1);
+    warp_limit = q_first < p.q_len ? p.first_len + min(q_first + QB - 1, p.q_len - 1) : 0;
   }
   float m_run[2] = {kNegBigM, kNegBigM}, l_run[2] = {0.0f, 0.0f};  // this lane's two columns (l: this lane's share)
 
@@ -363,7 +368,7 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
     for (int r = 0; r < 2; ++r) soff[r] = (row0 + g + 8 * r) * G * 4;
   };
   uint32_t koff[2], voff[2], soff[2];
-  make_offsets(16 * warp, koff, voff, soff);
+  make_offsets(PREFILL ? 0 : 16 * warp, koff, voff, soff);
 
   // One 16-token step of this warp.  kc / vc / ksc / vsc: shared-memory addresses of the tile's parts.
   // FULL: all 16 rows hold tokens (no validity selects); otherwise the first `valid` rows do, and the
@@ -511,8 +516,24 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
     const uint8_t* stage = smem + (it % kStagesM) * L::kStage;
     const int tok0 = (tile_begin + it) * kTileTok;
     const int rows = min(kTileTok, rl.ctx_len - tok0);
-    const int row0 = 16 * warp;
     const uint32_t sb = s2u(stage);
+    if (PREFILL) {
+#pragma unroll 1
+      for (int blk = 0; blk < kTileTok / 16; ++blk) {  // the warp's own positions over the whole tile
+        const int r16 = 16 * blk;
+        if (r16 >= rows || tok0 + r16 >= warp_limit) break;
+        const uint32_t cb = blk * (16 * 64);
+        const int sbo = blk * (16 * G * 4);
+        if (rows - r16 >= 16)
+          step16(std::true_type{}, sb + L::kKc + cb, sb + L::kVc + cb, stage + L::kKs + sbo, stage + L::kVs + sbo, koff, voff, soff,
+                 16, tok0 + r16);
+        else
+          step16(std::false_type{}, sb + L::kKc + cb, sb + L::kVc + cb, stage + L::kKs + sbo, stage + L::kVs + sbo, koff, voff,
+                 soff, rows - r16, tok0 + r16);
+      }
+      continue;
+    }
+    const int row0 = 16 * warp;
     if (rows - row0 >= 16)
       step16(std::true_type{}, sb + L::kKc, sb + L::kVc, stage + L::kKs, stage + L::kVs, koff, voff, soff, 16, tok0 + row0);
     else if (row0 < rows)
@@ -576,10 +597,14 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
       O = fmaf(s_acc[(w * RV + r) * kD + d], fct, O);
     }
     if (PREFILL) {
-      const int qi = q_first + r / R;
-      if (qi < p.q_len)
-        store_from_float(a.out, b * a.out_stride[0] + (hq0 + r % R) * a.out_stride[1] + qi * p.out_stride_t + d * a.out_stride[2],
-                         a.dtype, O / Lsum);
+      // every warp holds complete results for its own positions: nothing to merge
+#pragma unroll
+      for (int w = 0; w < kWarpsM; ++w) {
+        const int qi = cta_q_first + w * QB + r / R;
+        if (qi < p.q_len)
+          store_from_float(a.out, b * a.out_stride[0] + (hq0 + r % R) * a.out_stride[1] + qi * p.out_stride_t + d * a.out_stride[2],
+                           a.dtype, s_acc[(w * RV + r) * kD + d] / s_l[w][r]);
+      }
     } else if (p.splits == 1) {
       store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / Lsum);
     } else {
