@@ -567,7 +567,7 @@ def main() -> int:
         kf, vf = kk.repeat_interleave(4, dim=1), vv.repeat_interleave(4, dim=1)
         s2 = timed(lambda: F.scaled_dot_product_attention(qq, kf, vf, is_causal=True), 5, 3)
         sweep["int4_prefill_b8_q1024"] = {"us_per_launch": round(s / 5 * 1e6, 1), "torch_sdpa_bf16_us": round(s2 / 5 * 1e6, 1),
-                                          "cache_bytes_read": int(bb * 8 * 160 * sum(min(i + 2, tq) for i in range(0, tq, 2)))}
+                                          "cache_bytes_read": int(bb * 8 * 160 * sum(min(i + 8, tq) for i in range(0, tq, 8)))}
         del c, kk, vv, qq, kf, vf, pre_out
         torch.cuda.empty_cache()
         if rank == 0 and not args.no_cpu_baseline:
