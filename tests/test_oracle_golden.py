@@ -124,3 +124,23 @@ def test_ceil_log2_is_not_exact_ceiling():
     assert oracle.ceil_log2_f32(np.array([t]))[0] == -10.0
     assert oracle.ceil_log2_f32(np.array([np.float32(2.0 ** -10 * 1.001)]))[0] == -9.0
     assert oracle.ceil_log2_f32(np.array([np.nextafter(np.float32(1.0), np.float32(2.0))]))[0] == 1.0
+
+
+def test_prefill_oracle_is_the_decode_oracle_per_position():
+    """The causal prefill restatement must equal the decode restatement (pinned by the reference fixtures) run
+    on every query position alone."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(3)
+    b, hkv, ratio, tq, first, gs = 2, 2, 4, 9, 5, 32
+    total = first + tq - 1
+    k = rng.standard_normal((b, hkv, total, 128)).astype(np.float32)
+    v = rng.standard_normal((b, hkv, total, 128)).astype(np.float32)
+    kc, ks = oracle.int4_encode(k, gs)
+    vc, vs = oracle.int4_encode(v, gs)
+    kp, vp = oracle.int4_pack_nibbles(kc), oracle.int4_pack_nibbles(vc)
+    q = rng.standard_normal((b, hkv * ratio, tq, 128)).astype(np.float32)
+    whole = oracle.int4_prefill_attention(q, kp, vp, ks, vs, first, gs)
+    for i in range(tq):
+        one = oracle.int4_decode_attention(q[:, :, i], kp, vp, ks, vs, first + i, gs)
+        np.testing.assert_allclose(whole[:, :, i], one, rtol=1e-12, atol=1e-12)
