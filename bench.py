@@ -36,9 +36,10 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-# stdout carries exactly one JSON line: keep NCCL's version / info banner off it
-if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO", "TRACE"):
-    os.environ["NCCL_DEBUG"] = "WARN"  # also when unset: a system-wide nccl.conf may ask for the banner
+# The JSON line is the LAST line of stdout.  NCCL's log level is left as the environment sets it (a
+# launcher that asks for NCCL_DEBUG=INFO gets its rank / transport lines, on stdout or in NCCL_DEBUG_FILE);
+# only when nothing is set is the banner a system-wide nccl.conf might ask for kept quiet.
+os.environ.setdefault("NCCL_DEBUG", "WARN")
 
 HEADS, DIM, DSTATE, GROUPS, LAYERS = 128, 64, 128, 8, 24
 MX8_BYTES_PER_SEQ_LAYER = HEADS * DIM * (DSTATE // 16) * 18 * 2  # 2,359,296
@@ -109,35 +110,86 @@ class ClockSampler:
             self.result = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+REFERENCE_ARM_MAX_STEPS = 30
+
+
 def reference_arm(args, rank: int, world: int) -> int:
-    """The reference's CPU path for this workload on the box's host cores.  The reference has no CPU
-    code for the fused update itself, so this is the oracle's numpy restatement of its kernel."""
+    """The CPU arm: the hot path of this workload on the box's host cores.  The reference has no CPU
+    code for the fused update (its Triton kernels need a GPU; the interpreter is an oracle, not a
+    timing baseline), so what runs here is the oracle's numpy restatement of its kernel: kind "port".
+    One timed step = ONE of the step's 24 layers (`layers_timed`); `ms_per_step` is the time of that
+    one-layer sample, `value` its algorithmic GB/s."""
     if rank != 0:
         return 0
     import oracle.timing as ot
     cores = os.cpu_count() or 1
-    batch = 8
-    for _ in range(max(args.warmup, 0) and 1):
+    batch = args.batch_per_gpu
+    steps = max(1, min(args.steps, REFERENCE_ARM_MAX_STEPS))
+    warmup = max(0, min(args.warmup, 3))
+    for _ in range(warmup):
         ot.time_mx_update(batch, 8, threads=cores)
-    times = []
-    for _ in range(max(1, min(args.steps, 5))):
-        sec, used, nbytes = ot.time_mx_update(batch, 8, threads=cores)
+    times, draws = [], []
+    for _ in range(steps):
+        sec, used, nbytes, draw = ot.time_mx_update(batch, 8, threads=cores)
         times.append(sec)
+        draws.append(draw)
     sec = sum(times) / len(times)
     value = nbytes / sec / 1e9
-    sample = f"one of the step's 24 layers (batch {batch}, {nbytes} algorithmic bytes) per timed step, {len(times)} steps"
+    sample = (f"one of the step's 24 layers per timed step (batch {batch}, {nbytes} algorithmic bytes), numpy port of the "
+              f"reference kernel, {used} threads over (sequence, group) pieces")
     line = {
         "impl": "reference", "metric": "mx8_state_update_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": len(times), "warmup": 1 if args.warmup else 0, "ms_per_step": sec * 1e3 * LAYERS, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "layers_timed": 1, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus, batch, args.rng),
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": "port", "sample": sample},
+        "config": workload_config(args.gpus, batch, "reference"),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": "port", "sample": sample,
+                         "philox_draw_share": sum(draws) / sum(times)},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "ms_per_step extrapolates the sampled layer to the 24-layer step; the CPU arm draws the reference's own "
-                "Philox stream (one block per value) whatever --rng says",
+        "max_steps": REFERENCE_ARM_MAX_STEPS,
+        "note": "kind=port: a numpy restatement, NOT the reference's own code (which is Triton and needs a GPU; its kernels are "
+                "timed on the GPU in the sweep's triton_ref_* cells of the default arm).  A timed step is one layer, not the "
+                "24-layer step; the port always draws the reference's Philox stream (one block per value), and "
+                "philox_draw_share of its time goes into that draw.",
     }
     print(json.dumps(line), flush=True)
     return 0
+
+
+def triton_reference_cells(dev, peak: float) -> dict:
+    """The reference's own Triton kernels (unmodified, from baseline/_ref) compiled for and timed on this GPU,
+    with the same algorithmic byte counts as the library's cells.  A missing copy, a missing Triton or a
+    failure of the reference's code is reported in place of the numbers, never raised."""
+    try:
+        from baseline import reference, triton_cells as tc
+        if not reference.available():
+            return {"triton_ref": {"unavailable": "baseline/_ref is empty (python baseline/reference.py --from <Layer_Quant checkout>)"}}
+        import triton
+        ria, rmk = reference.load()
+    except Exception as exc:
+        return {"triton_ref": {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}}
+    import torch
+    out = {"triton_ref": {"triton": triton.__version__, "source": "baseline/_ref (unmodified phcool/Layer_Quant hybrid_quant/)",
+                          "note": "cache.step held fixed so the per-step recompile of the MX kernels is excluded (mx8_rejit_ms)"}}
+
+    def cell(name, fn):
+        try:
+            r = fn()
+            if "GBps" in r:
+                r["frac_of_hbm_peak"] = round(r["GBps"] / peak, 5)
+            out[name] = r
+        except Exception as exc:
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+
+    cell("triton_ref_int4_attn_b1_ctx1024_gs32", lambda: tc.decode_attention_cell(ria, 1, 1024, 32, dev))        # configuration 0
+    cell("triton_ref_int4_attn_b8_ctx2048_gs64", lambda: tc.decode_attention_cell(ria, 8, 2048, 64, dev))        # the published shape
+    cell("triton_ref_int4_attn_b16_ctx8192_gs32", lambda: tc.decode_attention_cell(ria, 16, 8192, 32, dev))
+    cell("triton_ref_int4_attn_b64_ctx32768_gs32", lambda: tc.decode_attention_cell(ria, 64, 32768, 32, dev, iters=2))
+    cell("triton_ref_mx8_update_b8", lambda: tc.mx8_update_cell(rmk, 8, LAYERS, dev, rejit=True))                # configuration 1
+    cell("triton_ref_mx8_update_b256", lambda: tc.mx8_update_cell(rmk, 256, 4, dev))
+    cell("triton_ref_mx4_update_b64", lambda: tc.mx4_update_cell(rmk, 64, 4, dev))                               # configuration 3
+    cell("triton_ref_mx4_update_b256", lambda: tc.mx4_update_cell(rmk, 256, 2, dev))
+    return out
 
 
 def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> dict:
@@ -276,6 +328,7 @@ def main() -> int:
     ap.add_argument("--case-batch", type=int, default=64)
     ap.add_argument("--case-ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-triton-ref", action="store_true", help="skip the sweep's triton_ref_* cells (the reference's kernels on this GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -394,9 +447,15 @@ def main() -> int:
     bytes_step = MX8_BYTES_PER_SEQ_LAYER * B * LAYERS
 
     results = {}
+    head_step = make_step(layers8, args.rng)
+    other = "reference" if args.rng == "layered" else "layered"
     with ClockSampler(local_rank) as clocks:
-        for name in (args.rng, "reference" if args.rng == "layered" else "layered"):  # headline stream first
-            results[name] = timed(make_step(layers8, name), args.steps, args.warmup)
+        results[args.rng] = timed(head_step, args.steps, args.warmup)  # the headline: exactly --steps steps
+        # The same step repeated for about a second (SUSTAINED_STEPS is fixed from the short run's rate), so that the
+        # 200 ms clock samples fall inside a timed region and an issue-bound kernel's clock is on record.
+        sustained_steps = int(min(20000, max(args.steps, 1.0 / max(results[args.rng] / args.steps, 1e-6))))
+        sustained_sec = timed(head_step, sustained_steps, 0)
+    results[other] = timed(make_step(layers8, other), args.steps, args.warmup)
     eager_sec = timed(make_step(layers8, args.rng, graph=False), args.steps, args.warmup)
     sec = results[args.rng]
     value = bytes_step * world * args.steps / sec / 1e9
@@ -499,41 +558,47 @@ def main() -> int:
                                                                "us_per_launch": round(s / 20 * 1e6, 1)}
             del big
             torch.cuda.empty_cache()
-        # the other batches of the MX4 comparison (one layer each, larger than L2) and the BF16 state it is compared with
-        for bb in (64, 1024):
-            big = make_layers(bb, 1, 4)
-            s = timed(make_step(big, "layered"), 5, 3)
-            gbs = MX4_BYTES_PER_SEQ_LAYER * bb * 5 / s / 1e9
-            sweep[f"mx4_update_b{bb}_layered_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
-                                                         "us_per_launch": round(s / 5 * 1e6, 1)}
+        # benchmark configuration 3: the MX4 update at batch 64 / 256 / 1024 x the step's 24 layers (library stream), and the
+        # BF16 state it is compared with (24 layers where they fit beside everything else, 4 at batch 1024: 8.6 GB,
+        # still far larger than L2)
+        for bb in (64, 256, 1024):
+            big = make_layers(bb, LAYERS, 4)
+            s = timed(make_step(big, "layered"), 3, 3)
+            gbs = MX4_BYTES_PER_SEQ_LAYER * bb * LAYERS * 3 / s / 1e9
+            sweep[f"mx4_update_b{bb}_x24_layered_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+                                                             "us_per_launch": round(s / (3 * LAYERS) * 1e6, 1),
+                                                             "ms_per_24_layer_step": round(s / 3 * 1e3, 3)}
             del big
             torch.cuda.empty_cache()
         from layer_quant_b200 import dense_state
-        for bb in (64, 256):
-            nlay = 4
+        for bb in (64, 256, 1024):
+            nlay = LAYERS if bb < 1024 else 4
             states = [torch.randn(bb, 128, 64, 128, generator=gen, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(nlay)]
             ops = make_layers(bb, 1, 8)[0][1]
             def dense_step():
                 for st in states:
                     dense_state.selective_state_update(st, ops["x"], ops["dt"], ops["A"], ops["B"], ops["C"], D=ops["D"],
                                                        dt_bias=ops["dt_bias"], dt_softplus=True, out=ops["out"])
-            s = timed(dense_step, 5, 3)
-            gbs = BF16_BYTES_PER_SEQ_LAYER * bb * nlay * 5 / s / 1e9
+            s = timed(dense_step, 3, 3)
+            gbs = BF16_BYTES_PER_SEQ_LAYER * bb * nlay * 3 / s / 1e9
             sweep[f"bf16_state_update_b{bb}"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
-                                                 "us_per_launch": round(s / (5 * nlay) * 1e6, 1)}
+                                                 "us_per_launch": round(s / (3 * nlay) * 1e6, 1), "layers": nlay}
             del states, ops
             torch.cuda.empty_cache()
-        for (bb, ctx) in ((1, 1024), (1, 131072), (8, 32768), (16, 8192), (64, 32768), (256, 8192)):
+        # benchmark configuration 2: batch {1, 16, 64, 256} x context {1k, 8k, 32k, 128k} (the largest cell holds 42.9 GB
+        # of cache), plus (8, 32k)
+        cells = [(bb, ctx) for bb in (1, 16, 64, 256) for ctx in (1024, 8192, 32768, 131072)] + [(8, 32768)]
+        for (bb, ctx) in cells:
             cap = ctx
             reps = max(1, int(np.ceil(4 * 126e6 / attn_bytes(bb, ctx))))  # distinct caches: >= 4x L2 in rotation
             reps = min(reps, 64)
             caches = []
             for _ in range(reps):
                 c = ia._allocate_layer_cache(bb, 8, cap, 128, 4, dev)
-                c.k_packed.copy_(torch.randint(0, 256, c.k_packed.shape, generator=gen, device=dev, dtype=torch.int16).to(torch.uint8))
-                c.v_packed.copy_(torch.randint(0, 256, c.v_packed.shape, generator=gen, device=dev, dtype=torch.int16).to(torch.uint8))
-                c.k_scale.copy_(torch.rand(c.k_scale.shape, generator=gen, device=dev) * 0.4 + 0.1)
-                c.v_scale.copy_(torch.rand(c.v_scale.shape, generator=gen, device=dev) * 0.4 + 0.1)
+                c.k_packed.random_(0, 256, generator=gen)  # in place: the largest cell has no room for temporaries
+                c.v_packed.random_(0, 256, generator=gen)
+                c.k_scale.uniform_(0.1, 0.5, generator=gen)
+                c.v_scale.uniform_(0.1, 0.5, generator=gen)
                 caches.append(c)
             q = randn(bb, 32, 1, 128)
             kn, vn = randn(bb, 8, 1, 128), randn(bb, 8, 1, 128)
@@ -570,6 +635,8 @@ def main() -> int:
                                           "cache_bytes_read": int(bb * 8 * 160 * sum(min(i + 8, tq) for i in range(0, tq, 8)))}
         del c, kk, vv, qq, kf, vf, pre_out
         torch.cuda.empty_cache()
+        if rank == 0 and world == 1 and not args.no_triton_ref:
+            sweep.update(triton_reference_cells(dev, peak))
         if rank == 0 and not args.no_cpu_baseline:
             # benchmark configuration 0 on the host cores, the reference's own CPU-runnable path: torch fake-quant of K / V
             # (int4_quant_dequant, group 32) + scaled_dot_product_attention, batch 1, 1024 tokens; beside it the
@@ -601,6 +668,15 @@ def main() -> int:
         cpu = {"value": nbytes / csec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
                "sample": "one layer of the step (batch 8, 18.9 MB algorithmic), numpy restatement of the reference kernel, one run"}
 
+    # DRAM bytes of one launch of the headline kernel: from the ncu capture summarised under profiles/ (a smaller
+    # batch, scaled by the batch: the kernel's traffic is proportional to it)
+    traffic, traffic_src = None, None
+    tj = ROOT / "profiles" / "mx8_state_update_traffic.json"
+    if tj.exists():
+        t = json.loads(tj.read_text())
+        traffic = (t["dram_bytes_read"] + t["dram_bytes_written"]) * B / t["batch"]
+        traffic_src = f"profiles/{tj.name}: ncu capture at batch {t['batch']}, scaled to batch {B}"
+
     if rank == 0:
         line = {
             "metric": "mx8_state_update_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -618,14 +694,13 @@ def main() -> int:
             "launch_mode": "24 update launches + 1 counter bump per step, replayed from a CUDA graph",
             "eager_launch": {"GBps": bytes_step * world * args.steps / eager_sec / 1e9, "ms_per_step": eager_sec / args.steps * 1e3},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # ncu capture at batch 64 (profiles/mx8_state_update_layered_batch64.md), scaled by batch:
-                         # 76.9 MB read + 18.8 MB written during the launch; the rest of the 75.5 MB of writes
-                         # leaves the 126 MB L2 after the kernel has ended
-                         "traffic": (76.9e6 + 18.8e6) * B / 64, "peak_source": peak_src,
+                         "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src,
                          "kernel": f"mx_state_update_fast_kernel<8, packed, {'PHILOX_LAYERED' if args.rng == 'layered' else 'PHILOX_REF'}, 128>",
                          "algorithmic_bytes_per_launch": MX8_BYTES_PER_SEQ_LAYER * B, "us_per_launch": per_launch_s * 1e6},
             "cpu_baseline": cpu,
             "clocks": clocks.result,
+            "sustained": {"steps": sustained_steps, "seconds": sustained_sec, "GBps": bytes_step * world * sustained_steps / sustained_sec / 1e9,
+                          "note": "the headline step repeated for about a second inside the clock-sampled region"},
             "streams": {k: {"GBps": bytes_step * world * args.steps / v / 1e9, "ms_per_step": v / args.steps * 1e3} for k, v in results.items()},
             "sweep": sweep,
         }

@@ -1,6 +1,10 @@
 """Generate tests/golden/*.npz by running the UNMODIFIED reference (phcool/Layer_Quant) on CPU.
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py --reference /path/to/Layer_Quant
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py --reference /path/to/Layer_Quant --check
+
+``--check`` regenerates every fixture into a temporary directory and compares it array by array
+with the committed files (exit status 1 on any difference); nothing in the tree is written.
 
 The reference's Triton kernels are executed by Triton's interpreter (numpy on CPU); its torch
 helpers run as they are.  Every file stores the inputs and the reference's outputs, so the
@@ -243,25 +247,101 @@ def gen_attention(out: Path, ia):
         print("attn", name, flush=True)
 
 
+def gen_prefill(out: Path, ia):
+    """The reference's own causal kernel over the packed cache (_int4_prefill_attention_kernel,
+    launched through _prefill_attention): a kernel the reference defines but never calls."""
+    from oracle import int4_encode, int4_pack_nibbles
+    gen = torch.Generator().manual_seed(5)
+    cases = [("p70_gs32", 1, 4, 2, 70, 32), ("p33_gs64", 2, 8, 2, 33, 64), ("p17_g1", 1, 2, 2, 17, 128)]
+    for name, b, hq, hkv, t, gs in cases:
+        q = torch.randn(b, hq, t, 128, generator=gen).bfloat16().float()  # fp32 carrier -> fp32 output
+        k = torch.randn(b, hkv, t, 128, generator=gen).bfloat16()
+        v = torch.randn(b, hkv, t, 128, generator=gen).bfloat16()
+        sel = torch.rand(b, hkv, t, 128, generator=gen) < 0.01
+        k = torch.where(sel, torch.full_like(k, 8.0), k)
+        cap = max(16, 1 << int(np.ceil(np.log2(max(t, 1)))))
+        cache = ia._allocate_layer_cache(b, hkv, cap, 128, 128 // gs, torch.device("cpu"))
+        for t_ in (cache.k_packed, cache.v_packed):
+            t_.fill_(0x77)
+        for t_ in (cache.k_scale, cache.v_scale):
+            t_.fill_(1.0e3)
+        kq, ks = int4_encode(f32(k), gs)
+        vq, vs = int4_encode(f32(v), gs)
+        cache.k_packed[:, :, :t] = torch.from_numpy(int4_pack_nibbles(kq))
+        cache.v_packed[:, :, :t] = torch.from_numpy(int4_pack_nibbles(vq))
+        cache.k_scale[:, :, :t] = torch.from_numpy(ks)
+        cache.v_scale[:, :, :t] = torch.from_numpy(vs)
+        o = ia._prefill_attention(q, cache, hq // hkv, gs)
+        np.savez_compressed(out / f"prefill_{name}.npz", q=f32(q), k_packed=cache.k_packed.numpy(), v_packed=cache.v_packed.numpy(),
+                            k_scale=cache.k_scale.numpy(), v_scale=cache.v_scale.numpy(), out=f32(o),
+                            meta=np.array([b, hq, hkv, t, gs], dtype=np.int64))
+        print("prefill", name, flush=True)
+
+
+def compare_dirs(fresh: Path, committed: Path) -> int:
+    """Array-by-array comparison of two fixture directories; returns the number of differences."""
+    bad = 0
+    names = sorted(p.name for p in fresh.glob("*.npz"))
+    for name in names:
+        if not (committed / name).exists():
+            print(f"MISSING  {name}: not committed")
+            bad += 1
+            continue
+        a, b = np.load(fresh / name), np.load(committed / name)
+        if sorted(a.files) != sorted(b.files):
+            print(f"DIFFERENT {name}: array names differ")
+            bad += 1
+            continue
+        diff = [k for k in a.files if a[k].dtype != b[k].dtype or a[k].shape != b[k].shape
+                or a[k].tobytes() != b[k].tobytes()]
+        if diff:
+            print(f"DIFFERENT {name}: {diff}")
+            bad += 1
+        else:
+            print(f"identical {name} ({len(a.files)} arrays)")
+    return bad
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a phcool/Layer_Quant checkout (imported, never copied)")
-    ap.add_argument("--only", default="")
+    ap.add_argument("--only", default="", help="comma-separated subset of philox,codec,update,attn,prefill")
+    ap.add_argument("--check", action="store_true", help="regenerate into a temporary directory and compare with the committed files")
     args = ap.parse_args()
-    sys.path.insert(0, args.reference)
-    sys.path.insert(0, str(HERE.parents[1]))
+    ref = Path(args.reference).resolve()
+    root = HERE.parents[1]
+    # The reference checkout comes FIRST on the path: this repository has a package called hybrid_quant
+    # too (its drop-in aliases), which must not shadow the reference's.  The repository root goes last and
+    # only supplies `oracle` (the nibble layout used to fill the attention fixtures' caches).
+    sys.path[:] = [p for p in sys.path if Path(p or ".").resolve() != root]
+    sys.path.insert(0, str(ref))
+    sys.path.append(str(root))
     from hybrid_quant import int4_8b_attention as ia
     from hybrid_quant import mamba_state_8b_kernel as mk
-    assert Path(ia.__file__).resolve().is_relative_to(Path(args.reference).resolve()), ia.__file__
-    todo = args.only.split(",") if args.only else ["philox", "codec", "update", "attn"]
+    for mod in (ia, mk):
+        assert Path(mod.__file__).resolve().is_relative_to(ref), f"{mod.__name__} came from {mod.__file__}, not from the reference"
+    todo = args.only.split(",") if args.only else ["philox", "codec", "update", "attn", "prefill"]
+    out = HERE
+    tmp = None
+    if args.check:
+        import tempfile
+        tmp = tempfile.TemporaryDirectory()
+        out = Path(tmp.name)
     if "philox" in todo:
-        gen_philox(HERE)
+        gen_philox(out)
     if "codec" in todo:
-        gen_codec(HERE, mk)
+        gen_codec(out, mk)
     if "update" in todo:
-        gen_update(HERE, mk)
+        gen_update(out, mk)
     if "attn" in todo:
-        gen_attention(HERE, ia)
+        gen_attention(out, ia)
+    if "prefill" in todo:
+        gen_prefill(out, ia)
+    if args.check:
+        bad = compare_dirs(out, HERE)
+        tmp.cleanup()
+        print("check:", "FAILED" if bad else "all regenerated fixtures are bit-identical to the committed ones")
+        sys.exit(1 if bad else 0)
 
 
 if __name__ == "__main__":

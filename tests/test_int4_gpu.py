@@ -368,3 +368,22 @@ def test_prefill_over_the_quantised_cache(gs, ratio, tq, first):
         m._prefill_attention(t(q, torch.bfloat16), cache, cache.k_packed.shape[2] + 1, ratio, gs)  # runs past the capacity
     from layer_quant_b200 import _lib
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["p70_gs32", "p33_gs64", "p17_g1"])
+def test_prefill_matches_reference_kernel_fixture(golden_dir, name):
+    """lq_int4_prefill_attn on the very cache bytes the reference's _int4_prefill_attention_kernel was run on
+    (under the interpreter): outputs within the fp32 bar of the reference kernel's own fp32 outputs."""
+    m = ia()
+    g = np.load(golden_dir / f"prefill_{name}.npz")
+    b, hq, hkv, tq, gs = (int(v) for v in g["meta"])
+    cap = g["k_packed"].shape[2]
+    cache = m._allocate_layer_cache(b, hkv, cap, 128, 128 // gs, dev())
+    cache.k_packed.copy_(t(g["k_packed"]))
+    cache.v_packed.copy_(t(g["v_packed"]))
+    cache.k_scale.copy_(t(g["k_scale"]))
+    cache.v_scale.copy_(t(g["v_scale"]))
+    cache.length = tq
+    out = m._prefill_attention(t(g["q"], torch.float32), cache, 1, hq // hkv, gs)
+    assert_out_close(out, g["out"])
+    assert_out_close(m._prefill_attention(t(g["q"], torch.bfloat16), cache, 1, hq // hkv, gs), g["out"])

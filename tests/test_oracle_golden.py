@@ -118,6 +118,18 @@ def test_decode_attention_matches_reference_kernel(golden_dir, name):
     assert np.abs(o - ref).max() <= 2e-5 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("name", ["p70_gs32", "p33_gs64", "p17_g1"])
+def test_prefill_attention_matches_reference_kernel(golden_dir, name):
+    """The reference's own causal kernel over the packed cache (_int4_prefill_attention_kernel, run under the
+    interpreter through _prefill_attention) against the prefill restatement."""
+    g = np.load(golden_dir / f"prefill_{name}.npz")
+    b, hq, hkv, t, gs = (int(v) for v in g["meta"])
+    o = oracle.int4_prefill_attention(g["q"], g["k_packed"], g["v_packed"], g["k_scale"], g["v_scale"], 1, gs)
+    ref = g["out"]  # fp32 output of the reference kernel
+    assert ref.shape == (b, hq, t, 128)
+    assert np.abs(o - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
 def test_ceil_log2_is_not_exact_ceiling():
     # a few ulps above a power of two the rounded fp32 logarithm is still the integer
     t = np.nextafter(np.float32(2.0 ** -10), np.float32(1.0))
