@@ -664,9 +664,11 @@ def main() -> int:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle.timing as ot
-        csec, cores, nbytes = ot.time_mx_update(8, 8, threads=os.cpu_count() or 1)
+        csec, cores, nbytes, cdraw = ot.time_mx_update(B, 8, threads=os.cpu_count() or 1, repeats=3)
         cpu = {"value": nbytes / csec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-               "sample": "one layer of the step (batch 8, 18.9 MB algorithmic), numpy restatement of the reference kernel, one run"}
+               "sample": f"one layer of the step (batch {B}, {nbytes / 1e6:.1f} MB algorithmic), numpy restatement of the reference "
+                         f"kernel (NOT the reference's own code), best of 3 runs, {cores} threads over (sequence, group) pieces",
+               "philox_draw_share": cdraw / csec}
 
     # DRAM bytes of one launch of the headline kernel: from the ncu capture summarised under profiles/ (a smaller
     # batch, scaled by the batch: the kernel's traffic is proportional to it)

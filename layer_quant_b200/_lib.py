@@ -11,8 +11,11 @@ from pathlib import Path
 
 import torch
 
+import os
+
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "liblayer_quant_b200.so"
+#: the shared library; LAYER_QUANT_B200_LIB selects another build of it (same ABI), e.g. one compiled with other options
+LIB_PATH = Path(os.environ.get("LAYER_QUANT_B200_LIB") or PKG / "liblayer_quant_b200.so")
 
 LQ_OK = 0
 LQ_ERR_INVALID_ARGUMENT = -1
