@@ -463,11 +463,15 @@ def main() -> int:
     per_launch_s = sec / (args.steps * LAYERS)
     achieved = MX8_BYTES_PER_SEQ_LAYER * B / per_launch_s / 1e9
 
-    # ---- end to end: host buffers in, host buffer out, through the public calls -------------------------
-    # (a) per call: mx_state_selective_update once per layer with fresh copies of its operands, the way the
-    #     reference's decode loop calls it; (b) prepared: the step's operands of all layers in ONE pinned host
-    #     buffer, copied in pieces that overlap the 24 prepared launches (MxUpdatePlan), outputs copied back
-    #     piece by piece, everything replayed from a CUDA graph.  (b) is what a serving loop gets: `e2e`.
+    # ---- end to end: host buffers in, host buffer out, through the reference's own call signature ----------
+    # Every variant calls mx_state_selective_update(cache, x, dt, A, B, C, D=, dt_bias=, dt_softplus=) once per layer, as
+    # the reference's decode loop does.  The step's x / dt / B / C of all layers sit in ONE pinned host buffer.
+    #   e2e           the 24 calls and the copies recorded once in a CUDA graph (the caches in graph mode: their step lives
+    #                 in a device counter, prepare_graph_decode's mechanism) and replayed per step: copies in four pieces of
+    #                 six layers on a copy stream, each piece's outputs copied back on a third stream
+    #   e2e.per_call  the same calls launched eagerly every step (one host-to-device copy per layer in, one out)
+    #   e2e.prepared  the graph built from prepared launches (MxUpdatePlan) that share one step counter: what the call
+    #                 itself costs beyond the kernel is the difference
     shapes = (("x", (B, HEADS, DIM)), ("dt", (B, HEADS)), ("B", (B, GROUPS, DSTATE)), ("C", (B, GROUPS, DSTATE)))
     per_layer = sum(int(np.prod(sh)) for _, sh in shapes)
     host_all = torch.randn(LAYERS * per_layer).to(torch.bfloat16).pin_memory()
@@ -485,62 +489,71 @@ def main() -> int:
 
     h2d = host_all.numel() * host_all.element_size()
     d2h = host_out_all.numel() * host_out_all.element_size()
-
-    def e2e_per_call_step():
-        for li, (cache, o) in enumerate(layers8):
-            hi, di = views(host_all, li), views(dev_all, li)
-            for k in hi:
-                di[k].copy_(hi[k], non_blocking=True)
-            y = mk.mx_state_selective_update(cache, di["x"], di["dt"][:, :, None].expand(B, HEADS, DIM), o["A"], di["B"], di["C"],
-                                             D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True, stochastic=True, seed=0,
-                                             rng_stream=args.rng)
-            host_out_all[li].copy_(y, non_blocking=True)
-
-    sec_e2e_call = timed(e2e_per_call_step, args.steps, args.warmup)
-
     e2e_layers = []
     for li, (cache, o) in enumerate(layers8):
         di = views(dev_all, li)
         e2e_layers.append((cache, dict(o, x=di["x"], dt=di["dt"][:, :, None].expand(B, HEADS, DIM), B=di["B"], C=di["C"], out=out_all[li])))
+
+    def call_layer(cache, o):
+        return mk.mx_state_selective_update(cache, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"],
+                                            dt_softplus=True, stochastic=True, seed=0, rng_stream=args.rng, out=o["out"])
+
+    def e2e_per_call_step():
+        for li, (cache, o) in enumerate(e2e_layers):
+            lo = li * per_layer
+            dev_all[lo:lo + per_layer].copy_(host_all[lo:lo + per_layer], non_blocking=True)
+            host_out_all[li].copy_(call_layer(cache, o), non_blocking=True)
+
+    sec_e2e_call = timed(e2e_per_call_step, args.steps, args.warmup)
+
     # The step's operands travel in E2E_CHUNKS pieces (6 layers each) on a copy stream while the previous piece is
-    # computed, and each piece's outputs leave on a third stream as soon as its launches are done; copies, the 24
-    # prepared launches and the counter bump are one CUDA graph.
+    # computed, and each piece's outputs leave on a third stream as soon as its launches are done.
     E2E_CHUNKS = 4
     lpc = LAYERS // E2E_CHUNKS
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def e2e_graph_of(launch_layer, after_step):
+        def body():
+            main = torch.cuda.current_stream(dev)
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+            for c in range(E2E_CHUNKS):
+                lo, hi = c * lpc * per_layer, (c + 1) * lpc * per_layer
+                with torch.cuda.stream(s_in):
+                    dev_all[lo:hi].copy_(host_all[lo:hi], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                main.wait_event(ev)
+                for li in range(c * lpc, (c + 1) * lpc):
+                    launch_layer(li)
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    host_out_all[c * lpc:(c + 1) * lpc].copy_(out_all[c * lpc:(c + 1) * lpc], non_blocking=True)
+            after_step()
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        body()
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body()
+        return g
+
     e2e_plans = [mk.MxUpdatePlan(cache, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"], dt_softplus=True,
                                  stochastic=True, seed=0, rng_stream=args.rng, out=o["out"], step_counter=counter)
                  for cache, o in e2e_layers]
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-
-    def e2e_body():
-        main = torch.cuda.current_stream(dev)
-        s_in.wait_stream(main)
-        s_out.wait_stream(main)
-        for c in range(E2E_CHUNKS):
-            lo, hi = c * lpc * per_layer, (c + 1) * lpc * per_layer
-            with torch.cuda.stream(s_in):
-                dev_all[lo:hi].copy_(host_all[lo:hi], non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-            main.wait_event(ev)
-            for pl in e2e_plans[c * lpc:(c + 1) * lpc]:
-                pl.run()
-            done = torch.cuda.Event()
-            done.record(main)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                host_out_all[c * lpc:(c + 1) * lpc].copy_(out_all[c * lpc:(c + 1) * lpc], non_blocking=True)
-        mk.advance_step_counter(counter)
-        main.wait_stream(s_in)
-        main.wait_stream(s_out)
-
-    e2e_body()
-    torch.cuda.synchronize(dev)
-    e2e_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(e2e_graph):
-        e2e_body()
-    e2e_step = e2e_graph.replay
-
+    g_prepared = e2e_graph_of(lambda li: e2e_plans[li].run(), lambda: mk.advance_step_counter(counter))
+    sec_e2e_prepared = timed(g_prepared.replay, args.steps, args.warmup)
+    del g_prepared
+    # graph mode of the public call: each cache's step moves to a device counter the call advances on the stream
+    for cache, _ in e2e_layers:
+        cache.step_counter = torch.full((1,), int(cache.step), dtype=torch.int64, device=dev)
+        cache.step = 0
+    g_calls = e2e_graph_of(lambda li: call_layer(*e2e_layers[li]), lambda: None)
+    e2e_step = g_calls.replay
     sec_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e_value = bytes_step * world * args.steps / sec_e2e / 1e9
 
@@ -686,13 +699,16 @@ def main() -> int:
             "dtype": "f32", "data": "synthetic", "config": workload_config(world, B, args.rng),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3,
-                    "mode": "pinned-host -> device copies of the step's x/dt/B/C in 4 pieces of 6 layers on a copy stream, the 24 "
-                            "prepared launches (MxUpdatePlan), device -> pinned-host copies of each piece's y on a third "
-                            "stream; all of it one CUDA graph per step",
+                    "mode": "mx_state_selective_update (the reference's call signature) once per layer, caches in graph mode; pinned-host "
+                            "-> device copies of the step's x/dt/B/C in 4 pieces of 6 layers on a copy stream, device -> pinned-host "
+                            "copies of each piece's y on a third stream; calls and copies recorded once in a CUDA graph, replayed per step",
                     "per_call": {"value": bytes_step * world * args.steps / sec_e2e_call / 1e9,
                                  "ms_per_step": sec_e2e_call / args.steps * 1e3,
-                                 "mode": "mx_state_selective_update called per layer, 4 copies in + 1 out per call"}},
-            "gpu_launches": args.steps * (LAYERS + 1),
+                                 "mode": "the same 24 calls launched eagerly every step, one copy in and one out per layer"},
+                    "prepared": {"value": bytes_step * world * args.steps / sec_e2e_prepared / 1e9,
+                                 "ms_per_step": sec_e2e_prepared / args.steps * 1e3,
+                                 "mode": "the graph built from prepared launches (MxUpdatePlan) sharing one step counter"}},
+            "gpu_launches": args.steps * (LAYERS + 1),  # the device-resident timed region: 24 updates + 1 counter bump per step
             "launch_mode": "24 update launches + 1 counter bump per step, replayed from a CUDA graph",
             "eager_launch": {"GBps": bytes_step * world * args.steps / eager_sec / 1e9, "ms_per_step": eager_sec / args.steps * 1e3},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -231,11 +231,17 @@ int lq_int4_prefill_attn(const lq_int4_prefill_args* args, void* cuda_stream);
  * (lq_int4_static_scratch_bytes() bytes, about 4.4 MB, held by every GPU that loads the library
  * until the process exits).  This entry point has no counterpart in the reference.
  *   - Limit: batch * q_heads * splits <= LQ_INT4_STATIC_MAX_SLOTS.  With splits = 0 the library
- *     picks a split count inside the limit; an explicit splits beyond it is refused with
- *     LQ_ERR_WORKSPACE.  One split needs no scratch and is always accepted.
+ *     picks a split count inside the limit; an explicit splits is first capped like
+ *     lq_int4_decode_attn caps it (at the number of 64-token tiles and at 128) and refused with
+ *     LQ_ERR_WORKSPACE if it is still beyond the limit.  One split needs no scratch and is
+ *     always accepted.
  *   - It allocates nothing (no cudaMalloc / cudaFree / allocating library call).
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
- *     with that device current); make that first call before any stream capture begins.
+ *     with that device current); make that first call before any stream capture begins.  The
+ *     array gets its device memory when the CUDA runtime loads the library's code onto that
+ *     device, which with lazy loading happens at that first call (or at the first launch of any
+ *     kernel of this library): make it before a memory pool takes what is left of the device
+ *     memory, or the load itself fails.
  *   - All calls on a device share the one array, which still holds the previous call's contents;
  *     the ticket counters are cleared on the stream before each launch.  Two calls that may overlap
  *     on the GPU (different streams) race on it: serialise them, or use lq_int4_decode_attn with

@@ -102,15 +102,16 @@ __device__ __forceinline__ void dense_store16(void* base, int64_t off, bool vec,
   }
 }
 
-// h' = h * dA + B * dtx on 16 values and their share of <h', C>, two values per packed fp32x2 instruction (sm_100)
+// h' = h * dA + (B * dt) * x on 16 values and their share of <h', C>, two values per packed fp32x2 instruction (sm_100);
+// dB = B * dt rounded, dB * x rounded, one fused multiply-add: the association of the Triton kernel this restates
 __device__ __forceinline__ float dense_update_readout16(float (&hv)[16], const float (&Bv)[16], const float (&Cv)[16], float dA,
-                                                        float dtx) {
-  const float2 dA2 = make_float2(dA, dA), dtx2 = make_float2(dtx, dtx);
+                                                        float dt, float x) {
+  const float2 dA2 = make_float2(dA, dA), dt2 = make_float2(dt, dt), x2 = make_float2(x, x);
   float2 ya = make_float2(0.0f, 0.0f), yb = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
-    const float2 h0 = __ffma2_rn(make_float2(hv[i], hv[i + 1]), dA2, __fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dtx2));
-    const float2 h1 = __ffma2_rn(make_float2(hv[i + 2], hv[i + 3]), dA2, __fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dtx2));
+    const float2 h0 = __ffma2_rn(make_float2(hv[i], hv[i + 1]), dA2, __fmul2_rn(__fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dt2), x2));
+    const float2 h1 = __ffma2_rn(make_float2(hv[i + 2], hv[i + 3]), dA2, __fmul2_rn(__fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dt2), x2));
     hv[i] = h0.x; hv[i + 1] = h0.y; hv[i + 2] = h1.x; hv[i + 3] = h1.y;
     ya = __ffma2_rn(h0, make_float2(Cv[i], Cv[i + 1]), ya);
     yb = __ffma2_rn(h1, make_float2(Cv[i + 2], Cv[i + 3]), yb);
@@ -118,7 +119,7 @@ __device__ __forceinline__ float dense_update_readout16(float (&hv)[16], const f
   return (ya.x + ya.y) + (yb.x + yb.y);
 }
 
-// h' = h exp(A dt) + B (dt x) on one 16-value block, and the block's share of <h', C>
+// h' = h exp(A dt) + (B dt) x on one 16-value block, and the block's share of <h', C>
 struct DenseRowCtx {
   const lq_dense_update_args* a;
   const DenseDerived* d;
@@ -128,9 +129,8 @@ __device__ __forceinline__ float dense_row_update(const DenseRowCtx& c, float (&
                                                   int h, int p, float xv, float dt_h, float dA_h) {
   const lq_dense_update_args& a = *c.a;
   if (c.d->dt_uniform && c.d->a_scalar) {
-    const float dtx = dt_h * xv;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA_h + Bv[i] * dtx;
+    for (int i = 0; i < 16; ++i) hv[i] = fmaf(hv[i], dA_h, __fmul_rn(__fmul_rn(Bv[i], dt_h), xv));
   } else {
     float dt = dt_h;
     if (!c.d->dt_uniform) {
@@ -138,16 +138,15 @@ __device__ __forceinline__ float dense_row_update(const DenseRowCtx& c, float (&
       if (a.dt_bias) dt += load_as_float(a.dt_bias, h * a.dt_bias_stride[0] + p * a.dt_bias_stride[1], a.dt_bias_dtype);
       if (a.dt_softplus) dt = softplus_ref(dt);
     }
-    const float dtx = dt * xv;
     if (c.d->a_scalar) {
       const float dA = expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) hv[i] = hv[i] * dA + Bv[i] * dtx;
+      for (int i = 0; i < 16; ++i) hv[i] = fmaf(hv[i], dA, __fmul_rn(__fmul_rn(Bv[i], dt), xv));
     } else {
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (c.n0 + i) * a.A_stride[2], a.A_dtype);
-        hv[i] = hv[i] * expf(Ai * dt) + Bv[i] * dtx;
+        hv[i] = fmaf(hv[i], expf(Ai * dt), __fmul_rn(__fmul_rn(Bv[i], dt), xv));
       }
     }
   }
@@ -401,7 +400,7 @@ __global__ void __launch_bounds__(kDenseThreads, 4) dense_state_update_ring_kern
     const int srow = chh * P + crow;
     if (active) {
       if (SIMPLE) {
-        y = dense_update_readout16(hv, Bv, Cv, dA_h, dt_h * sx[srow]);
+        y = dense_update_readout16(hv, Bv, Cv, dA_h, dt_h, sx[srow]);
       } else {
         y = dense_row_update(rc, hv, Bv, Cv, h0 + chh, crow, sx[srow], dt_h, dA_h);
       }

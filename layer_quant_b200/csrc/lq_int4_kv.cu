@@ -14,6 +14,7 @@
 // splits are merged with the usual (max, sum, output) rule.  The CTA that arrives last at a
 // per-(batch, kv head) ticket counter merges the splits, so no second launch and no waiting.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -911,19 +912,20 @@ constexpr size_t kStaticScratchBytes =
     kTicketBytes + LQ_INT4_STATIC_MAX_SLOTS * 2 * sizeof(float) + LQ_INT4_STATIC_MAX_SLOTS * kHeadDim * sizeof(float);
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-// The array's name is only a host-side handle; the device address has to be asked for, per device.
+// The array's name is only a host-side handle; the device address has to be asked for, per device.  Several host
+// threads may make the first call on a device at once: each looks the address up and publishes the same value.
 static int static_scratch_address(void** out) {
-  static void* cached[64] = {nullptr};
+  static std::atomic<void*> cached[64];
   int dev = 0;
   LQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(LQ_ERR_UNSUPPORTED, "lq_int4_decode_attn_static: device index %d out of range", dev);
-  if (cached[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     LQ_CHECK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
     if (p == nullptr) return fail(LQ_ERR_CUDA, "lq_int4_decode_attn_static: no device address for the built-in scratch");
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = p;
   return LQ_OK;
 }
 }  // namespace lq
@@ -940,10 +942,15 @@ LQ_EXPORT int lq_int4_decode_attn_static(const lq_int4_decode_args* args, void* 
   const int64_t per_split = static_cast<int64_t>(c.batch) * a.q_heads;
   const int64_t max_splits = static_cast<int64_t>(LQ_INT4_STATIC_MAX_SLOTS) / per_split;
   int splits = a.splits;
+  const int ctx_len = std::max(a.seq_len - (a.k_new ? 1 : 0), 1);
   if (splits <= 0) {  // library's choice, kept inside what the built-in scratch can hold
-    splits = pick_splits(c.batch, c.kv_heads, std::max(a.seq_len - (a.k_new ? 1 : 0), 1));
+    splits = pick_splits(c.batch, c.kv_heads, ctx_len);
     if (splits > max_splits) splits = static_cast<int>(std::max<int64_t>(max_splits, 1));
-  } else if (splits > 1 && splits > max_splits) {
+  } else {
+    // an explicit count is used as lq_int4_decode_attn would use it: never more splits than 64-token tiles, nor than 128
+    splits = std::min(splits, std::min((ctx_len + kTile - 1) / kTile, 128));
+  }
+  if (splits > 1 && splits > max_splits) {
     return fail(LQ_ERR_WORKSPACE,
                 "lq_int4_decode_attn_static: batch %d x %d query heads x %d splits = %lld partial results exceed the built-in "
                 "scratch (%d); use fewer splits or lq_int4_decode_attn with a caller-provided workspace",

@@ -162,18 +162,19 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
   micro_bits = __float_as_uint(macc + 8388608.0f) & 0xFFu;
 }
 
-// h' = h * dA + B * dtx on 16 values and the block's share of <h', C>, with packed fp32x2 instructions
+// h' = h * dA + (B * dt) * x on 16 values and the block's share of <h', C>, with packed fp32x2 instructions
 // (sm_100: two IEEE fp32 results per instruction, same rounding per component as the scalar forms).
-// Association as everywhere in this library: t = B * dtx rounded, then fma(h, dA, t); the read-out keeps
-// four partial sums over i mod 4, added as (y0 + y1) + (y2 + y3).
+// Association as in the reference kernel (mamba_state_8b_kernel.py:158, dB = B * dt, then state * dA + dB * x):
+// dB rounded, t = dB * x rounded, then fma(h, dA, t), which is what a compiler that contracts the reference's
+// expression produces; the read-out keeps four partial sums over i mod 4, added as (y0 + y1) + (y2 + y3).
 __device__ __forceinline__ float mx_update_readout16(float (&hv)[16], const float (&Bv)[16], const float (&Cv)[16], float dA,
-                                                     float dtx) {
-  const float2 dA2 = make_float2(dA, dA), dtx2 = make_float2(dtx, dtx);
+                                                     float dt, float x) {
+  const float2 dA2 = make_float2(dA, dA), dt2 = make_float2(dt, dt), x2 = make_float2(x, x);
   float2 ya = make_float2(0.0f, 0.0f), yb = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
-    const float2 t0 = __fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dtx2);
-    const float2 t1 = __fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dtx2);
+    const float2 t0 = __fmul2_rn(__fmul2_rn(make_float2(Bv[i], Bv[i + 1]), dt2), x2);
+    const float2 t1 = __fmul2_rn(__fmul2_rn(make_float2(Bv[i + 2], Bv[i + 3]), dt2), x2);
     const float2 h0 = __ffma2_rn(make_float2(hv[i], hv[i + 1]), dA2, t0);
     const float2 h1 = __ffma2_rn(make_float2(hv[i + 2], hv[i + 3]), dA2, t1);
     hv[i] = h0.x; hv[i + 1] = h0.y; hv[i + 2] = h1.x; hv[i + 3] = h1.y;

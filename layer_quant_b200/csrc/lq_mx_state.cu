@@ -254,17 +254,16 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
         mx_decode_block(codes, cur.e, cur.mic, hv);
         const float xv = sxh[p];
         if (hoisted) {
-          y = mx_update_readout16(hv, Bv, Cv, dA_h, dt_h * xv);  // h' = h exp(A dt) + B (dt x)
+          y = mx_update_readout16(hv, Bv, Cv, dA_h, dt_h, xv);  // h' = h exp(A dt) + (B dt) x
         } else {
           const float dt = d.dt_uniform ? dt_h : row_dt(h, p);
-          const float dtx = dt * xv;
           if (d.a_scalar) {
-            y = mx_update_readout16(hv, Bv, Cv, expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt), dtx);
+            y = mx_update_readout16(hv, Bv, Cv, expf(load_as_float(a.A, h * a.A_stride[0], a.A_dtype) * dt), dt, xv);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float Ai = load_as_float(a.A, h * a.A_stride[0] + p * a.A_stride[1] + (n0 + i) * a.A_stride[2], a.A_dtype);
-              hv[i] = fmaf(hv[i], expf(Ai * dt), Bv[i] * dtx);
+              hv[i] = fmaf(hv[i], expf(Ai * dt), __fmul_rn(__fmul_rn(Bv[i], dt), xv));
             }
             float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
 #pragma unroll
@@ -423,8 +422,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
       IO::codes_of(cur, codes);
       float hv[16];
       mx_decode_block(codes, cur.e, cur.mic, hv);
-      const float dtx = dt_h * sx[row];  // h' = h exp(A dt) + B (dt x)
-      float y = mx_update_readout16(hv, Bv, Cv, dA_h, dtx);
+      float y = mx_update_readout16(hv, Bv, Cv, dA_h, dt_h, sx[row]);  // h' = h exp(A dt) + (B dt) x
 
       const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
       uint32_t e_new, mic_new;

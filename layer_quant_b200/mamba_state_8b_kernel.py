@@ -23,16 +23,20 @@ Differences a caller can see, all opt-out:
   ``cache.to_layout("reference")`` converts.  The decoded values are identical.
 * MX4 works through ``mx_state_selective_update`` (the reference's wrapper raises TypeError for it)
   and needs no fp32 temporary.
-* ``RNG_STREAM = "reference"`` (default) draws exactly the reference's Philox numbers
-  (``tl.rand(seed, step * numel + index)``); ``"layered"`` uses the cheaper library stream keyed
-  on (seed, layer, step, index).
+* Stochastic rounding draws the library's own Philox stream, keyed on (seed, layer, step, block
+  index), unless ``rng_stream="reference"`` is passed to the call or to
+  ``patch_nemotron_h_mamba_decode_state_kernel`` (or ``RNG_STREAM`` is set): that reproduces the
+  reference's ``tl.rand(seed, step * numel + index)`` numbers and rounding rule bit for bit at
+  about a quarter of the speed (one Philox block per value instead of one per 16 values).
+* Repeated calls with the same operand tensors (the decode loop) reuse the argument block prepared
+  by the first call; only the output pointer and the step change.
 * A decode step never recompiles anything (the reference re-JITs each step because its RNG offset
   is a compile-time constant).
 """
 from __future__ import annotations
 
 import ctypes as ct
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from types import SimpleNamespace
 
 import torch
@@ -48,8 +52,13 @@ MX4_MANTISSA_MAX = 7.0
 
 #: storage layout new caches get: "packed" (native) or "reference" (the reference's tensors)
 DEFAULT_STATE_LAYOUT = "packed"
-#: random stream of stochastic rounding: "reference" (bit-identical to tl.rand) or "layered"
-RNG_STREAM = "reference"
+#: Random stream of stochastic rounding when neither the call nor the patch function names one:
+#: "layered"   one Philox4x32-10 block per 16-value MX block keyed on (seed, layer, step, block index), 8 random bits per
+#:             value, fixed-point rounding rule (LQ_ROUND_PHILOX_LAYERED): the fast stream, different layers draw
+#:             different numbers;
+#: "reference" exactly the reference's numbers and rule, ``tl.rand(seed, step * numel + index)`` with one Philox block per
+#:             value and no layer term (LQ_ROUND_PHILOX_REF): bit-for-bit the reference's codes, about four times slower.
+RNG_STREAM = "layered"
 
 _LAYOUTS = {"reference": _lib.LQ_MX_LAYOUT_REFERENCE, "packed": _lib.LQ_MX_LAYOUT_PACKED}
 
@@ -66,6 +75,10 @@ class MambaStateKernelCache:
     # Not in the reference: the step count kept on the device (one int64) once prepare_graph_decode has
     # run; the kernel adds it to ``step`` when it runs, so a recorded launch draws fresh numbers on replay.
     step_counter: torch.Tensor | None = None
+    # Not in the reference: the argument block prepared by the last mx_state_selective_update call on this cache
+    # and the operand signature it was prepared for.
+    _plan: object = field(default=None, repr=False, compare=False)
+    _plan_key: object = field(default=None, repr=False, compare=False)
 
     @property
     def state_shape(self) -> tuple[int, int, int, int]:
@@ -266,6 +279,14 @@ class MxUpdatePlan:
         self._fn = _lib.lib().lq_mx_state_update
         self._ref = ct.byref(a)
 
+    def rebind_out(self, out: torch.Tensor) -> None:
+        """Point the prepared call at another output tensor (shape and dtype of ``x``)."""
+        self.out = out
+        a = self.args
+        a.out = out.data_ptr()
+        a.out_stride[0], a.out_stride[1], a.out_stride[2] = out.stride()
+        a.out_dtype = _lib.dtype_code(out)
+
     def run(self) -> torch.Tensor:
         r = self.args.rounding
         step = int(self.cache.step)
@@ -317,12 +338,32 @@ def mx_state_selective_update(
     ``h_out`` (fp32 [B,H,P,N]) receives the updated state before requantisation; ``out`` is
     written instead of a fresh tensor.  :class:`MxUpdatePlan` prepares the same call once for
     loops that repeat it."""
-    y = MxUpdatePlan(cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus, stochastic=stochastic,
-                     seed=seed, rng_stream=rng_stream, rand_words=rand_words, h_out=h_out, out=out,
-                     step_counter=cache.step_counter).run()
+    # The decode loop calls this with the same tensors every step: the prepared argument block of the previous call is
+    # reused when every operand still has the same address, strides, dtype and shape.
+    key = (_sig(x), _sig(dt), _sig(A), _sig(B), _sig(C), _sig(D), _sig(z), _sig(dt_bias), _sig(rand_words), _sig(h_out),
+           _sig(cache.q_state), _sig(cache.shared_exp), _sig(cache.micro_exp), _sig(cache.step_counter),
+           bool(dt_softplus), bool(stochastic), int(seed), rng_stream or RNG_STREAM, cache.layout, cache.format_bits, cache.layer)
+    plan = cache._plan if cache._plan_key == key else None
+    if out is None:
+        out = torch.empty_like(x)
+    if plan is None:
+        plan = MxUpdatePlan(cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus, stochastic=stochastic,
+                            seed=seed, rng_stream=rng_stream, rand_words=rand_words, h_out=h_out, out=out,
+                            step_counter=cache.step_counter)
+        cache._plan, cache._plan_key = plan, key
+    else:
+        if out.shape != x.shape:
+            raise ValueError(f"Expected out shape {tuple(x.shape)}, got {tuple(out.shape)}")
+        plan.rebind_out(out)
+    y = plan.run()
     if cache.step_counter is not None:
         advance_step_counter(cache.step_counter)
     return y
+
+
+def _sig(t):
+    """What a prepared argument block depends on in one operand: address, strides, dtype, shape."""
+    return None if t is None else (t.data_ptr(), t.stride(), t.dtype, t.shape)
 
 
 def prepare_graph_decode(model) -> None:
@@ -359,14 +400,21 @@ def patch_nemotron_h_mamba_decode_state_kernel(
     group_size: int = MX8_BLOCK_SIZE,
     stochastic: bool = True,
     seed: int = 1234,
+    *,
+    rng_stream: str | None = None,
 ) -> None:
     """Route the remote modeling module's global ``selective_state_update`` through the MX kernels
     for every state tensor registered by :func:`register_mamba_state_kernel_caches`; any other
-    state falls through to the original function (reference :732-767)."""
+    state falls through to the original function (reference :732-767).  ``rng_stream`` (keyword-only,
+    not in the reference) fixes the random stream of the patched calls: "layered" or "reference";
+    None leaves it to ``RNG_STREAM`` at call time."""
+    if rng_stream not in (None, "layered", "reference"):
+        raise ValueError(f"unknown rng_stream {rng_stream!r}")
     module = _remote_module(model)
     original = getattr(module, "_mx_state_kernel_original", module.selective_state_update)
     module._mx_state_kernel_stochastic = stochastic
     module._mx_state_kernel_seed = seed
+    module._mx_state_kernel_rng_stream = rng_stream
 
     def selective_state_update_mx(ssm_state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False):
         kernel_cache = getattr(module, "_mamba_decode_state_kernel_caches", {}).get(id(ssm_state))
@@ -376,6 +424,7 @@ def patch_nemotron_h_mamba_decode_state_kernel(
             kernel_cache, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus,
             stochastic=getattr(module, "_mx_state_kernel_stochastic", True),
             seed=getattr(module, "_mx_state_kernel_seed", 1234),
+            rng_stream=getattr(module, "_mx_state_kernel_rng_stream", None),
         )
 
     if not getattr(module, "_mx_state_kernel_patched", False):

@@ -1,13 +1,19 @@
 """CPU restatement of the unquantised Mamba2 decode step (TEST INFRASTRUCTURE ONLY): the dense-state
 selective update and the causal-conv1d update.
 
-PARITY UNPINNED.  The algorithms live in third-party dependencies that are absent from the reference
-tree and from this machine: mamba-ssm==2.3.2.post1 (``mamba_ssm/ops/triton/selective_state_update.py``)
-and causal-conv1d==1.6.2.post1 (``causal_conv1d_update``), both pinned in the reference's
-``requirements.txt:7-8``.  What is restated here is their published behaviour for one decode token,
-anchored on the reference's call site (``hybrid_quant/mamba_state_8b_kernel.py:743-761`` hands the
-same ten arguments to either this update or the MX one) and on the reference's MX kernel, whose fp32
-update expression it shares (``mamba_state_8b_kernel.py:135-166``).
+The algorithms live in third-party dependencies that are absent from the reference tree and from this
+machine: mamba-ssm==2.3.2.post1 (``mamba_ssm/ops/triton/selective_state_update.py``) and
+causal-conv1d==1.6.2.post1 (``causal_conv1d_update``), both pinned in the reference's
+``requirements.txt:7-8``.  What is restated here is their published behaviour for one decode token.
+
+``dense_state_update`` is pinned for the un-gated case (z = None) through the reference's own MX
+kernels: the reference hands the same ten arguments to either update
+(``hybrid_quant/mamba_state_8b_kernel.py:743-761``), and its MX kernels evaluate the same fp32 expression
+(``:135-166``) on the decoded state before they requantise it.  Fed the decoded initial state of the
+reference-run fixtures (``tests/golden/update_*.npz``), this function must reproduce their y and, where the
+fixture keeps it, their fp32 h' (``tests/test_oracle_golden.py``).  PARITY UNPINNED for the rest: the gate
+``y * z * sigmoid(z)`` of the third-party update and the whole of ``causal_conv1d_update`` have no
+execution of their own code to be checked against here.
 """
 from __future__ import annotations
 
@@ -38,7 +44,7 @@ def dense_state_update(state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_s
     Ch = np.repeat(np.asarray(C, dtype=F32), ratio, axis=1)[:, :, None, :]
     with np.errstate(over="ignore", under="ignore"):
         dA = np.exp(np.asarray(A, dtype=F32)[None] * dt[..., None])
-        h = (state * dA + Bh * (dt * x)[..., None]).astype(F32)
+        h = (state * dA + (Bh * dt[..., None]) * x[..., None]).astype(F32)  # dB = B * dt, then dB * x
     y = (h.astype(np.float64) * Ch).sum(axis=-1)
     if D is not None:
         y = y + x * np.asarray(D, dtype=F32)[None]

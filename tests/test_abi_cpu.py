@@ -32,8 +32,11 @@ def test_every_declared_symbol_is_exported(lib):
 
 def test_struct_sizes_agree(lib):
     from layer_quant_b200 import _lib
-    for which, struct in enumerate((_lib.MxState, _lib.Rounding, _lib.MxUpdateArgs, _lib.Int4Cache, _lib.Int4DecodeArgs)):
-        assert lib.lq_abi_sizeof(which) == ct.sizeof(struct)
+    structs = (_lib.MxState, _lib.Rounding, _lib.MxUpdateArgs, _lib.Int4Cache, _lib.Int4DecodeArgs, _lib.DenseUpdateArgs,
+               _lib.Conv1dUpdateArgs, _lib.Int4PrefillArgs)
+    for which, struct in enumerate(structs):
+        assert lib.lq_abi_sizeof(which) == ct.sizeof(struct), struct.__name__
+    assert lib.lq_abi_sizeof(len(structs)) == -1
     assert lib.lq_abi_sizeof(99) == -1
     assert lib.lq_abi_version() == 1
 

@@ -122,3 +122,23 @@ def test_conv1d_update(dtype, width, act):
         m.causal_conv1d_update(t(x, dtype), conv_state, t(weight, dtype), None, "gelu")
     with pytest.raises(ValueError):
         m.causal_conv1d_update(t(x, dtype)[:, :7], conv_state, t(weight, dtype))
+
+
+@pytest.mark.parametrize("name", ["mx8_sr", "mx8_sr_nod", "mx4_sr"])
+def test_dense_update_against_reference_mx_fixtures(golden_dir, name):
+    """lq_dense_state_update on the decoded initial state of a reference-run MX fixture (an fp32 state, so the store
+    does not round): y within the fp32 bar of the reference kernel's y, h' within a few ulps of the MX4 pair's fp32 h'."""
+    from tests.test_oracle_golden import _dense_from_fixture
+    g = np.load(golden_dir / f"update_{name}.npz")
+    state_np, ops = _dense_from_fixture(g)
+    b, h, p, n = state_np.shape
+    state = t(state_np)
+    dt = t(np.ascontiguousarray(ops["dt"][:, :, 0]))[:, :, None].expand(b, h, p)
+    A = t(np.ascontiguousarray(ops["A"][:, 0, 0]))[:, None, None].expand(h, p, n)
+    D = None if ops["D"] is None else t(np.ascontiguousarray(ops["D"][:, 0]))[:, None].expand(h, p)
+    bias = None if ops["dt_bias"] is None else t(np.ascontiguousarray(ops["dt_bias"][:, 0]))[:, None].expand(h, p)
+    y = ds().selective_state_update(state, t(ops["x"]), dt, A, t(ops["B"]), t(ops["C"]), D=D, dt_bias=bias,
+                                    dt_softplus=ops["dt_softplus"])
+    assert_out_close(y, g["y0"])
+    if "h0" in g:
+        np.testing.assert_allclose(state.cpu().numpy(), g["h0"], rtol=3e-6, atol=1e-7)

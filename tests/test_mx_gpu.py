@@ -108,7 +108,7 @@ def test_dequantize_and_layout_roundtrip(bits):
     assert np.array_equal(cache.micro_exp.cpu().numpy()[0, 0], oracle.mx_pack_micro_bits(m))
 
 
-def run_update(m, d, bits, layout, stochastic=True, seed=0, steps=1, io_dtype=torch.bfloat16, softplus=True, rng_stream=None,
+def run_update(m, d, bits, layout, stochastic=True, seed=0, steps=1, io_dtype=torch.bfloat16, softplus=True, rng_stream="reference",
                words=None):
     cache = m.allocate_state_kernel_cache(t(d["state"]), 16, bits, layout=layout)
     ops = expand_update_operands(d, io_dtype)
@@ -154,6 +154,10 @@ def test_fused_update_against_reference_fixtures(path, layout):
         mism += int((q != g[f"q{s}"]).sum())
         assert np.abs(q.astype(np.int32) - g[f"q{s}"].astype(np.int32)).max() <= 1 + (s > 0)
         assert (e != g[f"e{s}"]).mean() < 0.01
+    # The reference run behind the fixture evaluates state * dA + dB * x with two roundings (the interpreter does not
+    # fuse) and numpy's exp; the kernel fuses the multiply-add as compiled Triton does.  Measured rate of differing
+    # codes: printed, and bounded.
+    print(f"codes differing from the interpreter run of the reference: {mism} of {total} = {mism / total:.2e} ({Path(path).name}, {layout})")
     assert mism / total < 5e-3, f"{mism} of {total} codes differ from the reference run"
 
 
@@ -258,7 +262,7 @@ def test_full_size_identity_step_is_idempotent(bits):
     y = m.mx_state_selective_update(cache, x0, dt, A0, B, C, stochastic=False)
     assert torch.equal(cache.q_state, snap[0]) and torch.equal(cache.shared_exp, snap[1]) and torch.equal(cache.micro_exp, snap[2])
     # stochastic rounding of exactly representable values cannot move them either
-    m.mx_state_selective_update(cache, x0, dt, A0, B, C, stochastic=True, seed=3)
+    m.mx_state_selective_update(cache, x0, dt, A0, B, C, stochastic=True, seed=3, rng_stream="reference")
     assert torch.equal(cache.q_state, snap[0]) and torch.equal(cache.shared_exp, snap[1])
     m.mx_state_selective_update(cache, x0, dt, A0, B, C, stochastic=True, seed=3, rng_stream="layered")
     assert torch.equal(cache.q_state, snap[0]) and torch.equal(cache.micro_exp, snap[2])
@@ -315,8 +319,8 @@ def test_dense_fast_path_equals_general_kernel(bits, layout):
     x, dt, A, B, C, D, z, bias = expand_update_operands(d)
     rng = np.random.default_rng(32)
     words = t(rng.integers(0, 2**32, size=(b, h, p, n), dtype=np.uint64).astype(np.uint32).view(np.int32))
-    for kw in (dict(stochastic=False), dict(stochastic=True, seed=5), dict(stochastic=True, seed=5, rng_stream="layered"),
-               dict(rand_words=words), dict(rand_words=words, rng_stream="layered")):
+    for kw in (dict(stochastic=False), dict(stochastic=True, seed=5, rng_stream="reference"), dict(stochastic=True, seed=5),
+               dict(rand_words=words, rng_stream="reference"), dict(rand_words=words, rng_stream="layered")):
         res = []
         for use_dump in (False, True):
             cache = m.allocate_state_kernel_cache(t(d["state"]), 16, bits, layout=layout)

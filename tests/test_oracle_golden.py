@@ -156,3 +156,31 @@ def test_prefill_oracle_is_the_decode_oracle_per_position():
     for i in range(tq):
         one = oracle.int4_decode_attention(q[:, :, i], kp, vp, ks, vs, first + i, gs)
         np.testing.assert_allclose(whole[:, :, i], one, rtol=1e-12, atol=1e-12)
+
+
+def _dense_from_fixture(g):
+    """Operands of the un-quantised update for a reference-run MX fixture: the decoded initial state as a dense fp32
+    state, everything else as the reference kernel was given it."""
+    bits, sp, stoch, seed, steps = (int(v) for v in g["meta"])
+    b, h, p, n = g["q_init"].shape
+    bias = None
+    if "dt_bias" in g:  # the MX kernel addresses dt_bias with D's strides: without D every head reads element 0
+        bias = np.broadcast_to(g["dt_bias"][:, None], (h, p)) if "D" in g else np.full((h, p), g["dt_bias"][0], np.float32)
+    state = oracle.mx_decode(g["q_init"], g["e_init"], g["m_init"])
+    ops = dict(x=g["x"], dt=np.broadcast_to(g["dt"][:, :, None], (b, h, p)), A=np.broadcast_to(g["A"][:, None, None], (h, p, n)),
+               B=g["B"], C=g["C"], D=np.broadcast_to(g["D"][:, None], (h, p)) if "D" in g else None, dt_bias=bias,
+               dt_softplus=bool(sp))
+    return state, ops
+
+
+@pytest.mark.parametrize("name", ["mx8_sr", "mx8_sr_nod", "mx4_sr"])
+def test_dense_update_oracle_is_pinned_by_the_reference_mx_kernels(golden_dir, name):
+    """The reference's MX kernels compute h' = h exp(A dt) + (B dt) x and y = <h', C> + D x in fp32 on the decoded state
+    before they requantise it: the same expression the un-quantised update evaluates.  Their y (and the MX4 pair's fp32
+    h', which the fixture keeps) therefore pin the dense-state restatement for the un-gated case."""
+    g = np.load(golden_dir / f"update_{name}.npz")
+    state, ops = _dense_from_fixture(g)
+    h, y = oracle.dense_state_update(state, **ops)
+    assert np.abs(y - g["y0"]).max() <= 2e-6 * np.abs(g["y0"]).max()
+    if "h0" in g:
+        assert np.array_equal(h, g["h0"])
