@@ -1,17 +1,16 @@
-"""A Nemotron-H-shaped hybrid model in torch, random-init, for running the patch functions and the
-decode kernels inside a model (tests at a small shape, ``bench.py --case model`` at the 8B shape).
+"""A Nemotron-H-shaped hybrid model in torch, random-init: TEST AND BENCHMARK STAND-IN, not product code.
 
-It stands in for the HuggingFace remote-code module the reference patches (the checkpoint, its
-modeling file, ``mamba_ssm`` and ``causal_conv1d`` are not available offline): same block layout
-(``backbone.layers[i].{block_type, norm, mixer, residual_in_fp32}``), same attribute names on the
-mixers, a module-global ``selective_state_update`` and ``repeat_kv``, and a
-``HybridMambaAttentionDynamicCache`` with ``conv_states`` / ``ssm_states`` lists -- everything
-``patch_nemotron_h_attention_int4_kv``, ``patch_nemotron_h_mamba_decode_state_kernel`` and
-``register_mamba_state_kernel_caches`` reach for.  Weights are random; the Mamba2 decode step
-follows the public Mamba2 formulation (in_proj -> causal conv1d update -> selective state update
--> gated RMSNorm -> out_proj), attention has no RoPE, the MLP is squared-ReLU.  On CUDA the two
-unquantised steps go through the library's baselines (``layer_quant_b200.dense_state``), the
-stand-ins for the third-party kernels the real module imports; on CPU they are plain torch.
+It stands in for the HuggingFace remote-code module the reference patches (the checkpoint, its modeling
+file, ``mamba_ssm`` and ``causal_conv1d`` are not available offline).  It loads the way the real one does,
+``AutoModelForCausalLM.from_pretrained(<this directory>, trust_remote_code=True)``, and has what the
+reference's scripts and patch functions reach for: the block layout
+(``backbone.layers[i].{block_type, norm, mixer, residual_in_fp32}``), the attribute names on the mixers,
+module-global ``selective_state_update`` and ``repeat_kv``, a ``HybridMambaAttentionDynamicCache`` with
+``conv_states`` / ``ssm_states`` lists, ``config.hybrid_override_pattern`` and ``config.conv_kernel``.
+The Mamba2 step follows the public Mamba2 formulation (in_proj -> causal conv1d update -> selective state
+update -> gated RMSNorm -> out_proj), attention has no RoPE, the MLP is squared-ReLU.  On CUDA the two
+unquantised steps go through the library's baselines (``layer_quant_b200.dense_state``), the stand-ins for
+the third-party kernels the real module imports; on CPU they are plain torch.
 """
 from __future__ import annotations
 
@@ -20,6 +19,9 @@ from types import SimpleNamespace
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+from transformers import PreTrainedModel
+
+from .configuration_nemotron_h_shim import NemotronHShimConfig, nemotron_h_8b_config, tiny_config  # noqa: F401
 
 
 def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
@@ -33,7 +35,7 @@ def selective_state_update(ssm_state, x, dt, A, B, C, D=None, z=None, dt_bias=No
     """Unquantised decode step on a floating-point state [B, H, P, N] (updated in place), fp32 math:
     the baseline the MX kernels are compared with (and the module-global symbol their patch replaces)."""
     if ssm_state.is_cuda and z is None:
-        from . import dense_state
+        from layer_quant_b200 import dense_state
         return dense_state.selective_state_update(ssm_state, x, dt, A, B, C, D=D, dt_bias=dt_bias, dt_softplus=dt_softplus)
     return selective_state_update_torch(ssm_state, x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, dt_softplus=dt_softplus)
 
@@ -73,6 +75,20 @@ class HybridMambaAttentionDynamicCache:
                 self.ssm_states.append(torch.zeros(batch_size, 0, device=device, dtype=dtype))
         self.key_cache = [None] * len(config.hybrid_override_pattern)  # bf16 KV of the unpatched attention
         self.value_cache = [None] * len(config.hybrid_override_pattern)
+        self.static_kv_len = 0  # > 0: key / value caches are pre-sized [B, Hkv, static_kv_len, D] and written in place
+
+    def presize_kv(self, max_len: int) -> None:
+        """Switch the unpatched attention to pre-sized K / V buffers of ``max_len`` rows (rows already cached are
+        kept): single-token steps then write row ``cache_position`` in place and attend under a length mask, so a
+        step allocates nothing and can be recorded in a CUDA graph."""
+        for i, k in enumerate(self.key_cache):
+            if k is None:
+                continue
+            v = self.value_cache[i]
+            nk, nv = k.new_zeros(k.shape[0], k.shape[1], max_len, k.shape[3]), v.new_zeros(v.shape[0], v.shape[1], max_len, v.shape[3])
+            nk[:, :, :k.shape[2]], nv[:, :, :v.shape[2]] = k, v
+            self.key_cache[i], self.value_cache[i] = nk, nv
+        self.static_kv_len = max_len
 
 
 class RMSNorm(nn.Module):
@@ -112,7 +128,7 @@ class Mamba2Mixer(nn.Module):
         gate, xbc, dt = self.in_proj(hs).split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)
         conv_state = cache_params.conv_states[self.layer_idx]
         if hs.is_cuda:
-            from . import dense_state
+            from layer_quant_b200 import dense_state
             xbc = dense_state.causal_conv1d_update(xbc, conv_state, self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
         else:
             conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
@@ -128,8 +144,33 @@ class Mamba2Mixer(nn.Module):
         return self.out_proj(self.norm(y.reshape(batch, -1), gate))
 
     def forward(self, hidden_states, cache_params=None, cache_position=None, attention_mask=None):
-        # prefill and decode alike: token by token (prompts in the tests are short)
-        return torch.stack([self._step(hidden_states[:, t], cache_params) for t in range(hidden_states.shape[1])], dim=1)
+        t_len = hidden_states.shape[1]
+        if t_len == 1:
+            return self._step(hidden_states[:, 0], cache_params).unsqueeze(1)
+        # Several tokens (a prompt): the projections, the convolution and the gated norm run over the whole sequence at
+        # once; only the state recurrence itself goes token by token through the same update the decode step uses.
+        import sys
+        module = sys.modules[__name__]
+        batch = hidden_states.shape[0]
+        gate, xbc, dt = self.in_proj(hidden_states).split([self.intermediate_size, self.conv_dim, self.num_heads], dim=-1)
+        conv_state = cache_params.conv_states[self.layer_idx]
+        full = torch.cat([conv_state, xbc.transpose(1, 2).to(conv_state.dtype)], dim=2)  # [B, C, W + T]
+        conv_state.copy_(full[:, :, -self.conv_kernel_size:])
+        windows = full[:, :, 1:].unfold(2, self.conv_kernel_size, 1)  # [B, C, T, W]: the window ending at each token
+        xbc = F.silu((windows.float() * self.conv1d.weight.squeeze(1).float()[None, :, None, :]).sum(-1)
+                     + self.conv1d.bias.float()[None, :, None]).to(hidden_states.dtype).transpose(1, 2)
+        x, B, C = xbc.split([self.intermediate_size, self.n_groups * self.ssm_state_size, self.n_groups * self.ssm_state_size], dim=-1)
+        A = (-torch.exp(self.A_log.float()))[:, None, None].expand(-1, self.head_dim, self.ssm_state_size)
+        D, bias = self.D[:, None].expand(-1, self.head_dim), self.dt_bias[:, None].expand(-1, self.head_dim)
+        state = cache_params.ssm_states[self.layer_idx]
+        ys = []
+        for t in range(t_len):
+            ys.append(module.selective_state_update(
+                state, x[:, t].reshape(batch, self.num_heads, self.head_dim), dt[:, t, :, None].expand(-1, -1, self.head_dim), A,
+                B[:, t].reshape(batch, self.n_groups, -1), C[:, t].reshape(batch, self.n_groups, -1), D, z=None, dt_bias=bias,
+                dt_softplus=True))
+        y = torch.stack(ys, dim=1).reshape(batch, t_len, -1)
+        return self.out_proj(self.norm(y, gate))
 
 
 class Attention(nn.Module):
@@ -152,6 +193,21 @@ class Attention(nn.Module):
         q = self.q_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(hidden_states).view(b, t, self.num_key_value_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(hidden_states).view(b, t, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        static = past_key_value is not None and getattr(past_key_value, "static_kv_len", 0) > 0 and t == 1
+        if static:
+            # pre-sized buffers: write row cache_position in place, attend all rows under a length mask (no allocation,
+            # no host read of the position: the step can be recorded in a CUDA graph)
+            pk, pv = past_key_value.key_cache[self.layer_idx], past_key_value.value_cache[self.layer_idx]
+            pos = cache_position.to(device=k.device, dtype=torch.long).reshape(1)
+            pk.index_copy_(2, pos, k)
+            pv.index_copy_(2, pos, v)
+            g = self.num_key_value_groups
+            qg = q.reshape(b, self.num_key_value_heads, g, self.head_dim)
+            scores = torch.einsum("bkgd,bktd->bkgt", qg, pk).float() * (self.head_dim ** -0.5)
+            hidden = torch.arange(pk.shape[2], device=k.device) > pos
+            probs = torch.softmax(scores.masked_fill(hidden, float("-inf")), dim=-1).to(pv.dtype)
+            out = torch.einsum("bkgt,bktd->bkgd", probs, pv).reshape(b, self.num_heads, 1, self.head_dim)
+            return self.o_proj(out.transpose(1, 2).reshape(b, t, -1)), None, past_key_value
         if past_key_value is not None:
             pk, pv = past_key_value.key_cache[self.layer_idx], past_key_value.value_cache[self.layer_idx]
             if pk is not None:
@@ -202,41 +258,36 @@ class Block(nn.Module):
         return residual + hidden_states
 
 
-class NemotronHShimForCausalLM(nn.Module):
+class NemotronHShimPreTrainedModel(PreTrainedModel):
+    config_class = NemotronHShimConfig
+    base_model_prefix = "backbone"
+    _no_split_modules = ["Block"]
+
+    def _init_weights(self, module):
+        std = self.config.initializer_range
+        if isinstance(module, (nn.Linear, nn.Conv1d)):
+            nn.init.normal_(module.weight, mean=0.0, std=std)
+            if module.bias is not None:
+                nn.init.zeros_(module.bias)
+        elif isinstance(module, nn.Embedding):
+            nn.init.normal_(module.weight, mean=0.0, std=std)
+
+
+class NemotronHShimForCausalLM(NemotronHShimPreTrainedModel):
     def __init__(self, config):
-        super().__init__()
-        self.config = config
+        super().__init__(config)
         self.backbone = nn.Module()
         self.backbone.embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
         self.backbone.layers = nn.ModuleList(Block(config, i, k) for i, k in enumerate(config.hybrid_override_pattern))
         self.backbone.norm_f = RMSNorm(config.hidden_size)
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
-
-    @property
-    def device(self):
-        return self.lm_head.weight.device
+        self.post_init()
 
     def forward(self, input_ids, cache_params=None, cache_position=None, use_cache=True, return_dict=True, attention_mask=None,
-                logits_to_keep=0):
+                logits_to_keep=0, **kwargs):
         h = self.backbone.embeddings(input_ids)
         for layer in self.backbone.layers:
             h = layer(h, cache_params=cache_params, cache_position=cache_position, attention_mask=attention_mask)
         if logits_to_keep:
             h = h[:, -logits_to_keep:]
         return SimpleNamespace(logits=self.lm_head(self.backbone.norm_f(h)))
-
-
-def nemotron_h_8b_config():
-    """The 8B shape: 52 blocks = 24 Mamba2 + 4 attention + 24 MLP, hidden 4096, vocab 131072, FFN 21504,
-    32 query / 8 kv heads of 128, Mamba2 with 128 heads of 64, state 128, 8 groups, conv kernel 4."""
-    return SimpleNamespace(
-        hybrid_override_pattern="M-M-M-M*-M-M-M-M-M*-M-M-M-M-M*-M-M-M-M-M*-M-M-M-M-M-", hidden_size=4096, vocab_size=131072,
-        intermediate_size=21504, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-        mamba_num_heads=128, mamba_head_dim=64, mamba_intermediate=8192, ssm_state_size=128, n_groups=8, conv_kernel=4)
-
-
-def tiny_config(pattern="M-M*-M-*M", hidden=256):
-    return SimpleNamespace(
-        hybrid_override_pattern=pattern, hidden_size=hidden, vocab_size=512, intermediate_size=2 * hidden,
-        num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-        mamba_num_heads=8, mamba_head_dim=64, mamba_intermediate=512, ssm_state_size=128, n_groups=2, conv_kernel=4)
