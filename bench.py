@@ -202,19 +202,20 @@ def workload_config(n_gpus: int, batch_per_gpu: int, rng: str = "reference") -> 
     }
 
 
-def model_case(args, dev, rank, world):
-    """benchmark configuration 4 in this repository's terms: a random-init Nemotron-H-8B-shaped model
-    (layer_quant_b200/nemotron_h_shim.py; projections, norms and MLP are torch library calls) decodes
-    ``--model-steps`` teacher-forced random tokens after a ``--model-prompt``-token prompt, first unpatched (bf16 KV
-    cache, bf16 SSM state through the library's dense-state kernel), then with INT4 KV (group 32) + MX8 state on every
-    Mamba2 layer, its whole decode step replayed from one CUDA graph.  Each rank holds ``--case-batch`` sequences.
-    Prints tokens/s of both runs and the KL divergence of the logits at the checkpoint steps."""
+def model_case(args, dev, rank, world, quiet=False):
+    """benchmark configuration 4 in this repository's terms: a random-init Nemotron-H-8B-shaped model (the stand-in of
+    tests/models/nemotron_h_shim; projections, norms and MLP are torch library calls) reads a ``--model-prompt``-token
+    random prompt and decodes ``--model-steps`` teacher-forced random tokens, ``--case-batch`` sequences per rank:
+    first unpatched (bf16 KV cache, bf16 SSM state through the library's dense-state kernel), then with INT4 KV
+    (group 32) + MX8 state on every Mamba2 layer.  BOTH arms replay their decode step from one CUDA graph (the bf16
+    arm on pre-sized K / V buffers), so the two differ only in the cache / state formats and their kernels.
+    Returns (and prints unless ``quiet``) tokens/s of both arms and the KL divergence of the logits at the checkpoints."""
     import torch
     import torch.distributed as dist
-    from layer_quant_b200 import int4_8b_attention as ia, mamba_state_8b_kernel as mk, nemotron_8b_decode_eval as ev
-    from layer_quant_b200 import nemotron_h_shim as shim, sharding
+    from layer_quant_b200 import _lib, int4_8b_attention as ia, mamba_state_8b_kernel as mk, sharding
+    from tests.models.nemotron_h_shim import modeling_nemotron_h_shim as shim
     cfg = shim.nemotron_h_8b_config() if args.model_shape == "8b" else shim.tiny_config()
-    bm, prompt, steps = args.case_batch, args.model_prompt, args.model_steps
+    bm, prompt, steps = args.model_batch, args.model_prompt, args.model_steps
     checkpoints = [c for c in (128, 256, 512, 1024, 2048) if c <= steps] or [steps]
     torch.manual_seed(0)
     old = torch.get_default_dtype()
@@ -229,7 +230,7 @@ def model_case(args, dev, rank, world):
     model.eval()
     nparams = sum(prm.numel() for prm in model.parameters())
     ids = torch.randint(0, cfg.vocab_size, (bm, prompt + steps + 1), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
-    mamba_layers, attn_layers, _ = ev.layer_groups(cfg)
+    mamba_layers = [i for i, kind in enumerate(cfg.hybrid_override_pattern) if kind == "M"]
 
     def timed_region(fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -244,49 +245,44 @@ def model_case(args, dev, rank, world):
 
     def decode(quantised):
         shim._mamba_decode_state_kernel_caches = {}
-        cache = ev.make_hybrid_cache(model, bm)
+        cache = shim.HybridMambaAttentionDynamicCache(cfg, bm, torch.bfloat16, device=dev)
         kept = {}
+        token = torch.zeros((bm, 1), dtype=ids.dtype, device=dev)
+        position = torch.zeros((1,), dtype=torch.long, device=dev)
         with torch.inference_mode():
-            model(ids[:, :prompt], cache_params=cache, cache_position=torch.arange(prompt), logits_to_keep=1)
-            if not quantised:
-                def step(st):
-                    pos = prompt + st
-                    out = model(ids[:, pos:pos + 1], cache_params=cache, cache_position=torch.tensor([pos]))
-                    if st + 1 in checkpoints:
-                        kept[st + 1] = out.logits[:, -1].float()
-
-                step(0)  # outside the timed region, like the quantised run's first step (library warm-up)
-
-                def run():
-                    for st in range(1, steps):
-                        step(st)
-                return timed_region(run), steps - 1, kept
-            mk.register_mamba_state_kernel_caches(model, cache, {i: "mx8" for i in mamba_layers})
-            ia.prepare_graph_decode(cache, prompt + steps)
-            mk.prepare_graph_decode(model)
-            token = torch.zeros((bm, 1), dtype=ids.dtype, device=dev)
+            model(ids[:, :prompt], cache_params=cache, cache_position=torch.arange(prompt, device=dev), logits_to_keep=1)
+            if quantised:
+                mk.register_mamba_state_kernel_caches(model, cache, {i: "mx8" for i in mamba_layers})
+                ia.prepare_graph_decode(cache, prompt + steps)
+                mk.prepare_graph_decode(model)
+                step_model = lambda: model(token, cache_params=cache)
+            else:
+                cache.presize_kv(prompt + steps)
+                step_model = lambda: model(token, cache_params=cache, cache_position=position)
             token.copy_(ids[:, prompt:prompt + 1])
-            first = model(token, cache_params=cache).logits[:, -1].float()  # step 1, eager (also warms every library up)
+            position.fill_(prompt)
+            first = step_model().logits[:, -1].float()  # step 1, eager (also warms every library up)
             if 1 in checkpoints:
                 kept[1] = first
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                static_logits = model(token, cache_params=cache).logits
+                static_logits = step_model().logits
 
             def run():
                 for st in range(1, steps):
                     token.copy_(ids[:, prompt + st:prompt + st + 1])
+                    position.fill_(prompt + st)
                     graph.replay()
                     if st + 1 in checkpoints:
                         kept[st + 1] = static_logits[:, -1].float().clone()
-            return timed_region(run), steps - 1, kept
+            sec = timed_region(run)
+        del graph
+        return sec, steps - 1, kept
 
     sec_base, n_base, logits_base = decode(False)
     ia.patch_nemotron_h_attention_int4_kv(model, group_size=32)
-    mk.RNG_STREAM = "layered"
-    mk.patch_nemotron_h_mamba_decode_state_kernel(model, 16, stochastic=True, seed=0)
+    mk.patch_nemotron_h_mamba_decode_state_kernel(model, 16, stochastic=True, seed=0, rng_stream=args.rng)
     sec_q, n_q, logits_q = decode(True)
-    from layer_quant_b200 import _lib
     status = _lib.device_status()
     kl = {}
     for c in checkpoints:
@@ -296,18 +292,20 @@ def model_case(args, dev, rank, world):
             dist.all_reduce(v)
             v = v / world
         kl[str(c)] = float(v)
-    if rank == 0:
-        print(json.dumps({
-            "case": "model", "shape": args.model_shape, "params": nparams, "n_gpus": world, "batch_per_gpu": bm,
-            "global_batch": bm * world, "prompt": prompt, "decode_steps": steps,
-            "tokens_per_s_int4kv_mx8_graph": bm * world * n_q / sec_q, "ms_per_step_int4kv_mx8_graph": sec_q / n_q * 1e3,
-            "tokens_per_s_bf16_eager": bm * world * n_base / sec_base, "ms_per_step_bf16_eager": sec_base / n_base * 1e3,
-            "kl_bf16_vs_quantised_at_step": kl, "device_status": status,
-            "note": "random-init weights ~N(0, 0.02), teacher-forced random tokens; projections / norms / MLP are torch "
-                    "library kernels; the bf16 run is launched eagerly (its growing KV cache cannot be recorded)"}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-    return 0
+    result = {
+        "case": "model", "shape": args.model_shape, "params": nparams, "n_gpus": world, "batch_per_gpu": bm,
+        "global_batch": bm * world, "prompt": prompt, "decode_steps": steps,
+        "tokens_per_s": bm * world * n_q / sec_q, "ms_per_step": sec_q / n_q * 1e3,
+        "tokens_per_s_bf16": bm * world * n_base / sec_base, "ms_per_step_bf16": sec_base / n_base * 1e3,
+        "kl_bf16_vs_quantised_at_step": kl, "device_status": status, "rng_stream": args.rng,
+        "note": "INT4 KV (group 32) + MX8 state on all 24 Mamba2 layers against the same model with bf16 KV and bf16 state; both "
+                "arms replay one CUDA graph per decode step; random-init weights ~N(0, 0.02), teacher-forced random tokens; "
+                "projections / norms / MLP are torch library kernels"}
+    del model
+    torch.cuda.empty_cache()
+    if rank == 0 and not quiet:
+        print(json.dumps(result), flush=True)
+    return result
 
 
 def main() -> int:
@@ -321,11 +319,13 @@ def main() -> int:
                     help="random stream of the headline number (both are always reported)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--model-prompt", type=int, default=1024, help="--case model: prompt length")
-    ap.add_argument("--model-steps", type=int, default=2048, help="--case model: decode steps")
+    ap.add_argument("--model-steps", type=int, default=0, help="model case: decode steps (default 2048 with --case model, 256 inside the default line)")
     ap.add_argument("--model-shape", default="8b", choices=["8b", "tiny"], help="--case model: Nemotron-H-8B shape or the test shape")
     ap.add_argument("--case", default="", choices=["", "mx8", "mx4", "attn", "bf16", "model"],
                     help="run only one small kernel case (for ncu captures): plain launches, no graph, no sweep")
     ap.add_argument("--case-batch", type=int, default=64)
+    ap.add_argument("--model-batch", type=int, default=32, help="model case: sequences per GPU")
+    ap.add_argument("--no-model", action="store_true", help="leave the model case (benchmark configuration 4) out of the default line")
     ap.add_argument("--case-ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true", help="skip the sweep's triton_ref_* cells (the reference's kernels on this GPU)")
@@ -410,7 +410,12 @@ def main() -> int:
         return sharding.all_reduce_max(e0.elapsed_time(e1) / 1e3, dev)
 
     if args.case == "model":
-        return model_case(args, dev, rank, world)
+        args.model_steps = args.model_steps or 2048
+        model_case(args, dev, rank, world)
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return 0
     if args.case:
         # one kernel, a few plain launches on a working set larger than L2 and at most a few GB
         cb = args.case_batch
@@ -683,6 +688,15 @@ def main() -> int:
                          f"kernel (NOT the reference's own code), best of 3 runs, {cores} threads over (sequence, group) pieces",
                "philox_draw_share": cdraw / csec}
 
+    # ---- benchmark configuration 4 at every N: the full decode step of the 8B-shaped model ---------------------------
+    model = None
+    if not args.no_model:
+        args.model_steps = args.model_steps or 256
+        try:
+            model = model_case(args, dev, rank, world, quiet=True)
+        except Exception as exc:  # the kernel-level line must survive a failure of the model-level case
+            model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     # DRAM bytes of one launch of the headline kernel: from the ncu capture summarised under profiles/ (a smaller
     # batch, scaled by the batch: the kernel's traffic is proportional to it)
     traffic, traffic_src = None, None
@@ -721,6 +735,7 @@ def main() -> int:
                           "note": "the headline step repeated for about a second inside the clock-sampled region"},
             "streams": {k: {"GBps": bytes_step * world * args.steps / v / 1e9, "ms_per_step": v / args.steps * 1e3} for k, v in results.items()},
             "sweep": sweep,
+            "model": model,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -338,11 +338,21 @@ def mx_state_selective_update(
     ``h_out`` (fp32 [B,H,P,N]) receives the updated state before requantisation; ``out`` is
     written instead of a fresh tensor.  :class:`MxUpdatePlan` prepares the same call once for
     loops that repeat it."""
+    # the reference's own checks, in its order (:615-621)
+    if cache.q_state.ndim != 4:
+        raise ValueError(f"Expected q_state [B,H,P,N], got {tuple(cache.q_state.shape)}")
+    if x.shape != cache.state_shape[:3]:
+        raise ValueError(f"Expected x shape {cache.state_shape[:3]}, got {tuple(x.shape)}")
+    if B.ndim != 3 or C.ndim != 3:
+        raise ValueError("Expected B and C with shape [batch, ngroups, dstate] for decode update.")
     # The decode loop calls this with the same tensors every step: the prepared argument block of the previous call is
-    # reused when every operand still has the same address, strides, dtype and shape.
-    key = (_sig(x), _sig(dt), _sig(A), _sig(B), _sig(C), _sig(D), _sig(z), _sig(dt_bias), _sig(rand_words), _sig(h_out),
-           _sig(cache.q_state), _sig(cache.shared_exp), _sig(cache.micro_exp), _sig(cache.step_counter),
-           bool(dt_softplus), bool(stochastic), int(seed), rng_stream or RNG_STREAM, cache.layout, cache.format_bits, cache.layer)
+    # reused when every operand still has the same address and strides (and x / B the same shape and type: with the
+    # state's shape they fix every other operand's shape).
+    key = (x.data_ptr(), x.stride(), x.shape, x.dtype, dt.data_ptr(), dt.stride(), dt.dtype, A.data_ptr(), A.stride(), A.dtype,
+           B.data_ptr(), B.stride(), B.shape, B.dtype, C.data_ptr(), C.stride(), C.dtype, _sig(D), _sig(z), _sig(dt_bias),
+           _sig(rand_words), _sig(h_out), cache.q_state.data_ptr(), cache.shared_exp.data_ptr(), cache.micro_exp.data_ptr(),
+           None if cache.step_counter is None else cache.step_counter.data_ptr(),
+           dt_softplus, stochastic, seed, rng_stream or RNG_STREAM, cache.layout, cache.format_bits, cache.layer)
     plan = cache._plan if cache._plan_key == key else None
     if out is None:
         out = torch.empty_like(x)
@@ -362,8 +372,8 @@ def mx_state_selective_update(
 
 
 def _sig(t):
-    """What a prepared argument block depends on in one operand: address, strides, dtype, shape."""
-    return None if t is None else (t.data_ptr(), t.stride(), t.dtype, t.shape)
+    """What a prepared argument block depends on in an optional operand: address, strides, type."""
+    return None if t is None else (t.data_ptr(), t.stride(), t.dtype)
 
 
 def prepare_graph_decode(model) -> None:

@@ -8,7 +8,7 @@ class NemotronHShimConfig(PretrainedConfig):
 
     model_type = "nemotron_h_shim"
 
-    def __init__(self, hybrid_override_pattern="M-M*-M-*M", hidden_size=256, vocab_size=512, intermediate_size=512,
+    def __init__(self, hybrid_override_pattern="M-M*-M-*M", hidden_size=1024, vocab_size=512, intermediate_size=2048,
                  num_attention_heads=8, num_key_value_heads=2, head_dim=128, mamba_num_heads=8, mamba_head_dim=64,
                  mamba_intermediate=512, ssm_state_size=128, n_groups=2, conv_kernel=4, initializer_range=0.05, **kwargs):
         self.hybrid_override_pattern = hybrid_override_pattern
@@ -32,5 +32,7 @@ def nemotron_h_8b_config() -> NemotronHShimConfig:
         initializer_range=0.02)
 
 
-def tiny_config(pattern="M-M*-M-*M", hidden=256) -> NemotronHShimConfig:
+def tiny_config(pattern="M-M*-M-*M", hidden=1024) -> NemotronHShimConfig:
+    """The test shape.  hidden = attention heads x head_dim (8 x 128), as in the real model: the reference's attention
+    forward reshapes its output to [batch, q_len, hidden_size] (int4_8b_attention.py:689,712)."""
     return NemotronHShimConfig(hybrid_override_pattern=pattern, hidden_size=hidden, intermediate_size=2 * hidden)

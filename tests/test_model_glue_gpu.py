@@ -1,5 +1,5 @@
 """The patch functions and the attention forward replacement running inside a model on the GPU: a
-small Nemotron-H-shaped torch model (layer_quant_b200/nemotron_h_shim.py) is decoded unpatched (bf16 KV, bf16
+small Nemotron-H-shaped torch model (tests/models/nemotron_h_shim) is decoded unpatched (bf16 KV, bf16
 SSM state) and patched (INT4 KV cache, MX8 / MX4 state), the way run_nemotron_8b_decode_degradation.py
 drives the real model: prefill, register the state caches, then one token per step."""
 import copy
@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from layer_quant_b200 import nemotron_h_shim as shim
+from tests.models.nemotron_h_shim import modeling_nemotron_h_shim as shim
 
 pytestmark = pytest.mark.gpu
 
