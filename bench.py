@@ -315,7 +315,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch-per-gpu", type=int, default=8)
-    ap.add_argument("--rng", default="layered", choices=["reference", "layered"],
+    ap.add_argument("--rng", default="layered", choices=["reference", "layered", "layered4"],
                     help="random stream of the headline number (both are always reported)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--model-prompt", type=int, default=1024, help="--case model: prompt length")
@@ -461,6 +461,7 @@ def main() -> int:
         sustained_steps = int(min(20000, max(args.steps, 1.0 / max(results[args.rng] / args.steps, 1e-6))))
         sustained_sec = timed(head_step, sustained_steps, 0)
     results[other] = timed(make_step(layers8, other), args.steps, args.warmup)
+    results["layered4"] = timed(make_step(layers8, "layered4"), args.steps, args.warmup)
     eager_sec = timed(make_step(layers8, args.rng, graph=False), args.steps, args.warmup)
     sec = results[args.rng]
     value = bytes_step * world * args.steps / sec / 1e9
@@ -569,7 +570,7 @@ def main() -> int:
         torch.cuda.empty_cache()
         for bits, per_seq in ((8, MX8_BYTES_PER_SEQ_LAYER), (4, MX4_BYTES_PER_SEQ_LAYER)):
             big = make_layers(256, 4, bits)
-            for name in ("reference", "layered"):
+            for name in ("reference", "layered4", "layered"):
                 s = timed(make_step(big, name), 5, 3)
                 gbs = per_seq * 256 * 4 * 5 / s / 1e9
                 sweep[f"mx{bits}_update_b256_{name}_stream"] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
@@ -646,7 +647,7 @@ def main() -> int:
         ia._pack_kv_into_cache(c, kk, vv, torch.arange(tq, device=dev), 32)
         qq = randn(bb, 32, tq, 128)
         pre_out = torch.empty_like(qq)
-        s = timed(lambda: ia._prefill_attention(qq, c, 1, 4, 32, out=pre_out), 5, 3)
+        s = timed(lambda: ia._prefill_attention(qq, c, 4, 32, out=pre_out), 5, 3)
         kf, vf = kk.repeat_interleave(4, dim=1), vv.repeat_interleave(4, dim=1)
         s2 = timed(lambda: F.scaled_dot_product_attention(qq, kf, vf, is_causal=True), 5, 3)
         sweep["int4_prefill_b8_q1024"] = {"us_per_launch": round(s / 5 * 1e6, 1), "torch_sdpa_bf16_us": round(s2 / 5 * 1e6, 1),

@@ -64,13 +64,19 @@ extern "C" {
  *                   block (counter = block index lo/hi, step, layer) per 16-value MX block, value i
  *                   takes byte i & 3 of word i >> 2 as an 8-bit uniform draw r8; fixed-point rule
  *                   q = floor(fl32(v/scale + 49152 + r8/256)) - 49152.  No reference counterpart.
- *   SUPPLIED_FIXED  the fixed-point rule with r8 = low 8 bits of caller-supplied words           */
+ *   SUPPLIED_FIXED  the fixed-point rule with r8 = low 8 bits of caller-supplied words
+ *   PHILOX_LAYERED4 the reference's rule, floor(a) + (u < a - floor(a)) with u mapped from a 32-bit word as
+ *                   tl.rand maps it, on the library's keying: one Philox4x32-10 block (counter = quad index
+ *                   lo/hi, step, layer) per FOUR values, value i of a quad takes word i.  It separates the two
+ *                   things PHILOX_LAYERED changes at once: this mode changes only where the numbers come from
+ *                   (all four words, a layer term), PHILOX_LAYERED also the rounding rule.                    */
 #define LQ_ROUND_HALF_UP 0
 #define LQ_ROUND_HALF_EVEN 1
 #define LQ_ROUND_PHILOX_REF 2
 #define LQ_ROUND_SUPPLIED 3
 #define LQ_ROUND_PHILOX_LAYERED 4
 #define LQ_ROUND_SUPPLIED_FIXED 5
+#define LQ_ROUND_PHILOX_LAYERED4 6
 
 typedef struct lq_mx_state {
   void* q_state;         /* device; see layouts above                                           */
@@ -86,9 +92,9 @@ typedef struct lq_mx_state {
 
 typedef struct lq_rounding {
   int32_t mode;          /* LQ_ROUND_*                                                           */
-  uint32_t layer;        /* PHILOX_LAYERED only                                                  */
+  uint32_t layer;        /* PHILOX_LAYERED / PHILOX_LAYERED4 only                                */
   uint64_t seed;         /* Philox key (low word k0, high word k1)                               */
-  uint64_t step;         /* PHILOX_LAYERED: counter word; PHILOX_REF: unused (see rng_offset)    */
+  uint64_t step;         /* PHILOX_LAYERED(4): counter word; PHILOX_REF: unused (see rng_offset) */
   uint64_t rng_offset;   /* PHILOX_REF: RNG_OFFSET = step * numel of the reference (:659, :716)  */
   const uint32_t* words; /* SUPPLIED / SUPPLIED_FIXED: device, one word per value, [B,H,P,N]   */
   const uint64_t* step_counter; /* optional device counter read when the kernel runs: its value is

@@ -27,7 +27,7 @@ LQ_ERR_DEVICE_STATUS = -5
 LQ_BF16, LQ_F16, LQ_F32 = 0, 1, 2
 LQ_MX_LAYOUT_REFERENCE, LQ_MX_LAYOUT_PACKED = 0, 1
 (LQ_ROUND_HALF_UP, LQ_ROUND_HALF_EVEN, LQ_ROUND_PHILOX_REF, LQ_ROUND_SUPPLIED, LQ_ROUND_PHILOX_LAYERED,
- LQ_ROUND_SUPPLIED_FIXED) = range(6)
+ LQ_ROUND_SUPPLIED_FIXED, LQ_ROUND_PHILOX_LAYERED4) = range(7)
 
 _DTYPES = {torch.bfloat16: LQ_BF16, torch.float16: LQ_F16, torch.float32: LQ_F32}
 

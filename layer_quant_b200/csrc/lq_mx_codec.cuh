@@ -39,7 +39,7 @@ __device__ __forceinline__ float mx_decode_scale(uint32_t e, uint32_t micro) {
 
 // Rounding context of one 16-value block.
 struct MxRoundCtx {
-  uint64_t counter;      // PHILOX_REF: counter of value 0 of the block; PHILOX_LAYERED: index of the block
+  uint64_t counter;      // PHILOX_REF: counter of value 0 of the block; PHILOX_LAYERED: index of the block; PHILOX_LAYERED4: of its first quad
   uint32_t wrap32;       // PHILOX_REF: counters are taken modulo 2^32 with a zero high word
   uint32_t step, layer;  // PHILOX_LAYERED
   const uint32_t* words; // SUPPLIED / SUPPLIED_FIXED: 16 words of this block
@@ -64,7 +64,7 @@ constexpr float kByteMagic = 49152.0f;  // 1.5 * 2^15: ulp 2^-8, mantissa bits 8
 // Encodes h[0..15].  codes[w] holds values 4w..4w+3 as int8 lanes; micro_bits bit i = pair i.
 //
 // Two rounding rules:
-//  * reference rule (HALF_UP, HALF_EVEN, PHILOX_REF, SUPPLIED): a = min(|h| / scale, M), level from
+//  * reference rule (HALF_UP, HALF_EVEN, PHILOX_REF, SUPPLIED, PHILOX_LAYERED4): a = min(|h| / scale, M), level from
 //    floor(a + .5) / rint(a) / floor(a) + (u < a - floor(a)), sign restored afterwards -- the
 //    reference's expressions, evaluated with the same fp32 operations;
 //  * fixed-point rule (PHILOX_LAYERED, SUPPLIED_FIXED): t = fl32(h / scale + 49152 + r8 / 256) in one
@@ -99,6 +99,14 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
     for (int i = 0; i < 4; ++i) {
       const uint4 v = __ldg(w4 + i);
       rnd[4 * i] = v.x; rnd[4 * i + 1] = v.y; rnd[4 * i + 2] = v.z; rnd[4 * i + 3] = v.w;
+    }
+  }
+  if (MODE == LQ_ROUND_PHILOX_LAYERED4) {  // one Philox block per four values, value i of a quad takes word i
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {
+      const uint64_t c = ctx.counter + qd;
+      const Philox4 r = philox4x32_10(static_cast<uint32_t>(c), static_cast<uint32_t>(c >> 32), ctx.step, ctx.layer, keys);
+      rnd[4 * qd] = r.w0; rnd[4 * qd + 1] = r.w1; rnd[4 * qd + 2] = r.w2; rnd[4 * qd + 3] = r.w3;
     }
   }
   uint32_t pw[4] = {0u, 0u, 0u, 0u};  // PHILOX_LAYERED: 16 random bytes, value i = byte i & 3 of word i >> 2
@@ -142,7 +150,7 @@ __device__ __forceinline__ void mx_encode_block(const float (&h)[16], const unsi
           lvl = rintf(a);
         } else {
           uint32_t w;
-          if (MODE == LQ_ROUND_SUPPLIED) {
+          if (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_PHILOX_LAYERED4) {
             w = rnd[i];
           } else {  // the reference's stream: one Philox block per value, word 0
             const uint64_t c = ctx.counter + i;

@@ -147,7 +147,7 @@ template <int MODE>
 __device__ __forceinline__ MxRoundCtx round_ctx_at(const MxRoundBase& b, uint64_t lin) {
   MxRoundCtx c;
   c.wrap32 = b.wrap32;
-  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 4) : (b.offset + lin);
+  c.counter = (MODE == LQ_ROUND_PHILOX_LAYERED) ? (lin >> 4) : (MODE == LQ_ROUND_PHILOX_LAYERED4) ? (lin >> 2) : (b.offset + lin);
   c.step = b.step;
   c.layer = b.layer;
   c.words = (MODE == LQ_ROUND_SUPPLIED || MODE == LQ_ROUND_SUPPLIED_FIXED) ? b.words + lin : nullptr;
@@ -571,7 +571,7 @@ static int validate_state(const lq_mx_state& s, const char* who) {
 }
 
 static int validate_rounding(const lq_rounding& r, const char* who) {
-  LQ_CHECK_ARG(r.mode >= LQ_ROUND_HALF_UP && r.mode <= LQ_ROUND_SUPPLIED_FIXED, "%s: unknown rounding mode %d", who, r.mode);
+  LQ_CHECK_ARG(r.mode >= LQ_ROUND_HALF_UP && r.mode <= LQ_ROUND_PHILOX_LAYERED4, "%s: unknown rounding mode %d", who, r.mode);
   if (r.mode == LQ_ROUND_SUPPLIED || r.mode == LQ_ROUND_SUPPLIED_FIXED) {
     LQ_CHECK_ARG(r.words != nullptr, "%s: rounding mode %d needs words", who, r.mode);
     LQ_CHECK_ARG(reinterpret_cast<uintptr_t>(r.words) % 16 == 0, "%s: rounding words must be 16-byte aligned", who);
@@ -643,6 +643,7 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
       case LQ_ROUND_PHILOX_REF: LQ_FAST_LAUNCH(LQ_ROUND_PHILOX_REF); break;
       case LQ_ROUND_SUPPLIED: LQ_FAST_LAUNCH(LQ_ROUND_SUPPLIED); break;
       case LQ_ROUND_PHILOX_LAYERED: LQ_FAST_LAUNCH(LQ_ROUND_PHILOX_LAYERED); break;
+      case LQ_ROUND_PHILOX_LAYERED4: LQ_FAST_LAUNCH(LQ_ROUND_PHILOX_LAYERED4); break;
       default: LQ_FAST_LAUNCH(LQ_ROUND_SUPPLIED_FIXED); break;
     }
 #undef LQ_FAST_LAUNCH
@@ -656,6 +657,7 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
     case LQ_ROUND_PHILOX_REF: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, smem, st>>>(a, d); break;
     case LQ_ROUND_SUPPLIED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, smem, st>>>(a, d); break;
     case LQ_ROUND_PHILOX_LAYERED: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, smem, st>>>(a, d); break;
+    case LQ_ROUND_PHILOX_LAYERED4: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED4><<<grid, block, smem, st>>>(a, d); break;
     default: mx_state_update_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, smem, st>>>(a, d); break;
   }
 }
@@ -672,6 +674,7 @@ static void launch_quantize_mode(const lq_mx_state& s, const void* src, int dt, 
     case LQ_ROUND_PHILOX_REF: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_REF><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
     case LQ_ROUND_SUPPLIED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
     case LQ_ROUND_PHILOX_LAYERED: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
+    case LQ_ROUND_PHILOX_LAYERED4: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_PHILOX_LAYERED4><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
     default: mx_quantize_kernel<BITS, LAYOUT, LQ_ROUND_SUPPLIED_FIXED><<<grid, block, 0, st>>>(s, src, dt, stride, r, keys, total); break;
   }
 }

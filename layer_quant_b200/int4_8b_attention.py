@@ -315,12 +315,13 @@ def _append_decode_attention(query_states, key_states, value_states, cache, seq_
 PREFILL_FROM_INT4_CACHE = False
 
 
-def _prefill_attention(query_states: torch.Tensor, cache: Int4KVLayerCache, first_len: int, num_key_value_groups: int,
-                       group_size: int, *, out: torch.Tensor | None = None) -> torch.Tensor:
+def _prefill_attention(query_states: torch.Tensor, cache: Int4KVLayerCache, num_key_value_groups: int, group_size: int, *,
+                       first_len: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of the q_len query positions of ``query_states`` [B, Hq, Tq, D] over cache rows that
     already hold their K / V: position i attends rows [0, first_len + i).  Returns [B, Hq, Tq, D] in the
-    query's dtype.  ``first_len = 1`` is a prompt from position 0 (the reference's unused
-    ``_int4_prefill_attention_kernel``, :114-251); larger values continue an existing context."""
+    query's dtype.  Positional arguments as the reference's ``_prefill_attention`` (:594-625, the launcher of its
+    unused ``_int4_prefill_attention_kernel``, :114-251), which is ``first_len = 1``: a prompt from position 0;
+    larger values (keyword-only, not in the reference) continue an existing context."""
     batch, n_heads, q_len, head_dim = query_states.shape
     if n_heads != cache.k_packed.shape[1] * num_key_value_groups:
         raise ValueError(f"{n_heads} query heads != {cache.k_packed.shape[1]} kv heads x {num_key_value_groups}")
@@ -423,7 +424,7 @@ def _forward_fused_int4_kv(self, hidden_states, attention_mask=None, position_id
     _pack_kv_into_cache(layer_cache, key_states, value_states, positions, group_size, known_len=required_len)
     if PREFILL_FROM_INT4_CACHE and attention_mask is None and group_size in (32, 64, 128):
         # contiguous positions ending at required_len - 1 (what _positions hands out for a prompt or a chunk)
-        attn = _prefill_attention(query_states, layer_cache, required_len - q_len + 1, self.num_key_value_groups, group_size)
+        attn = _prefill_attention(query_states, layer_cache, self.num_key_value_groups, group_size, first_len=required_len - q_len + 1)
         return self.o_proj(attn.transpose(1, 2).reshape(bsz, q_len, -1)), None, past_key_value
     k_full = self._int4_kv_repeat_kv(key_states, self.num_key_value_groups)
     v_full = self._int4_kv_repeat_kv(value_states, self.num_key_value_groups)

@@ -56,6 +56,8 @@ DEFAULT_STATE_LAYOUT = "packed"
 #: "layered"   one Philox4x32-10 block per 16-value MX block keyed on (seed, layer, step, block index), 8 random bits per
 #:             value, fixed-point rounding rule (LQ_ROUND_PHILOX_LAYERED): the fast stream, different layers draw
 #:             different numbers;
+#: "layered4"  the reference's rounding rule (floor(a) + (u < frac), 24-bit u) on the library's keying, one Philox block per
+#:             four values (LQ_ROUND_PHILOX_LAYERED4): between the two in cost, isolates the keying from the rule;
 #: "reference" exactly the reference's numbers and rule, ``tl.rand(seed, step * numel + index)`` with one Philox block per
 #:             value and no layer term (LQ_ROUND_PHILOX_REF): bit-for-bit the reference's codes, about four times slower.
 RNG_STREAM = "layered"
@@ -266,6 +268,8 @@ class MxUpdatePlan:
             r.mode = _lib.LQ_ROUND_PHILOX_REF
         elif stream == "layered":
             r.mode = _lib.LQ_ROUND_PHILOX_LAYERED
+        elif stream == "layered4":
+            r.mode = _lib.LQ_ROUND_PHILOX_LAYERED4
         else:
             raise ValueError(f"unknown rng_stream {stream!r}")
         if h_out is not None:
@@ -418,7 +422,7 @@ def patch_nemotron_h_mamba_decode_state_kernel(
     state falls through to the original function (reference :732-767).  ``rng_stream`` (keyword-only,
     not in the reference) fixes the random stream of the patched calls: "layered" or "reference";
     None leaves it to ``RNG_STREAM`` at call time."""
-    if rng_stream not in (None, "layered", "reference"):
+    if rng_stream not in (None, "layered", "layered4", "reference"):
         raise ValueError(f"unknown rng_stream {rng_stream!r}")
     module = _remote_module(model)
     original = getattr(module, "_mx_state_kernel_original", module.selective_state_update)

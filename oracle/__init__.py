@@ -23,7 +23,7 @@ from .mx_codec import (  # noqa: F401
     mx_encode, mx_decode, mx_pack_micro_bits, mx_unpack_micro_bits, mx4_pack_nibbles,
     mx4_unpack_nibbles, ceil_log2_f32, native_sr_encode,
 )
-from .mx_state import mx_state_update, reference_rng_offsets  # noqa: F401
+from .mx_state import mx_state_update, reference_rng_offsets, layered4_words  # noqa: F401
 from .int4_kv import (  # noqa: F401
     int4_encode, int4_decode, int4_pack_nibbles, int4_unpack_nibbles, int4_quant_dequant,
     int4_decode_attention, decode_attention_mask, int4_prefill_attention,

@@ -53,6 +53,18 @@ def layered_r8(seed: int, layer: int, step: int, shape) -> np.ndarray:
     return bytes_.reshape(-1)[:total].reshape(shape).astype(np.int64)
 
 
+def layered4_words(seed: int, layer: int, step: int, shape) -> np.ndarray:
+    """One 32-bit word per state value for LQ_ROUND_PHILOX_LAYERED4: one Philox4x32-10 block per four values,
+    counter = (quad_lo, quad_hi, step, layer), key = seed; value i of a quad takes word i.  The reference's rounding
+    rule is then fed ``words_to_uniform`` of these words."""
+    total = int(np.prod(shape))
+    quads = np.arange((total + 3) // 4, dtype=np.uint64)
+    s = int(seed) & 0xFFFFFFFFFFFFFFFF
+    w = philox4x32_10(s & 0xFFFFFFFF, s >> 32, quads & np.uint64(0xFFFFFFFF), quads >> np.uint64(32),
+                      int(step) & 0xFFFFFFFF, int(layer) & 0xFFFFFFFF)
+    return np.stack(w, axis=-1).astype(np.uint32).reshape(-1)[:total].reshape(shape)
+
+
 def mx_state_update(q_state, shared_exp, micro_exp, x, dt, A, B, C, D=None, z=None, dt_bias=None,
                     dt_softplus=False, format_bits=8, rounding="stochastic", seed=1234, step=0,
                     layer=0, rnd=None, r8=None, return_state=False):
@@ -62,7 +74,7 @@ def mx_state_update(q_state, shared_exp, micro_exp, x, dt, A, B, C, D=None, z=No
 
     rounding: 'stochastic' (reference Philox stream from seed/step, or ``rnd`` if supplied),
     'half_up' (reference deterministic), 'layered' (library stream from seed/layer/step, or
-    ``r8`` if supplied).
+    ``r8`` if supplied), 'layered4' (the reference's rule on the library's keying).
     Returns (y fp32 [B,H,P], q', shared_exp', micro_exp') and the fp32 state h' if asked."""
     mmax = 63 if format_bits == 8 else 7
     bsz, nh, dim, dstate = q_state.shape
@@ -86,7 +98,10 @@ def mx_state_update(q_state, shared_exp, micro_exp, x, dt, A, B, C, D=None, z=No
     if z is not None:
         y = y * np.asarray(z, dtype=F32)  # :163-165
     state = state.astype(F32)
-    if rounding == "layered":
+    if rounding == "layered4":
+        from .philox import words_to_uniform
+        q, e, m = mx_encode(state, mmax, "stochastic", words_to_uniform(layered4_words(seed, layer, step, state.shape)))
+    elif rounding == "layered":
         if r8 is None:
             r8 = layered_r8(seed, layer, step, state.shape)
         q, e, m = native_sr_encode(state, mmax, r8)

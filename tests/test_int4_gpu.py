@@ -355,17 +355,17 @@ def test_prefill_over_the_quantised_cache(gs, ratio, tq, first):
     cache = fill_cache(m, k, v, gs, capacity=(total + 5 + 15) // 16 * 16)  # scale rows of a head stay 16-byte aligned
     ref = oracle.int4_prefill_attention(q, *cache_np(cache), first, gs)
     for dtype in (torch.bfloat16, torch.float32):
-        out = m._prefill_attention(t(q, dtype), cache, first, ratio, gs)
+        out = m._prefill_attention(t(q, dtype), cache, ratio, gs, first_len=first)
         assert tuple(out.shape) == (b, hq, tq, 128) and out.dtype == dtype
         assert_out_close(out, ref)
     # the same through a strided query view ([B, Tq, Hq, D] storage, as the projections leave it)
     qs = t(np.ascontiguousarray(q.transpose(0, 2, 1, 3)), torch.bfloat16).transpose(1, 2)
-    assert_out_close(m._prefill_attention(qs, cache, first, ratio, gs), ref)
+    assert_out_close(m._prefill_attention(qs, cache, ratio, gs, first_len=first), ref)
     for i in (0, tq // 2, tq - 1):
         one = m._decode_attention(t(q[:, :, i:i + 1], torch.float32), cache, first + i, ratio, gs)
         assert_out_close(one, ref[:, :, i])
     with pytest.raises(ValueError):
-        m._prefill_attention(t(q, torch.bfloat16), cache, cache.k_packed.shape[2] + 1, ratio, gs)  # runs past the capacity
+        m._prefill_attention(t(q, torch.bfloat16), cache, ratio, gs, first_len=cache.k_packed.shape[2] + 1)  # runs past the capacity
     from layer_quant_b200 import _lib
     assert _lib.device_status() == 0
 
@@ -384,6 +384,6 @@ def test_prefill_matches_reference_kernel_fixture(golden_dir, name):
     cache.k_scale.copy_(t(g["k_scale"]))
     cache.v_scale.copy_(t(g["v_scale"]))
     cache.length = tq
-    out = m._prefill_attention(t(g["q"], torch.float32), cache, 1, hq // hkv, gs)
+    out = m._prefill_attention(t(g["q"], torch.float32), cache, hq // hkv, gs)
     assert_out_close(out, g["out"])
-    assert_out_close(m._prefill_attention(t(g["q"], torch.bfloat16), cache, 1, hq // hkv, gs), g["out"])
+    assert_out_close(m._prefill_attention(t(g["q"], torch.bfloat16), cache, hq // hkv, gs), g["out"])

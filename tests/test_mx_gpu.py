@@ -81,6 +81,11 @@ def test_codec_supplied_bits_and_library_stream(golden_dir, bits):
     q, e, m, _ = quantize(vals, bits, "reference", _lib.LQ_ROUND_PHILOX_LAYERED, seed=77, layer=5, step=9)
     qo, eo, mo = oracle.native_sr_encode(vals, mmax, layered_r8(77, 5, 9, vals.shape))
     assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(m, mo)
+    # the reference's rounding rule on the library's keying: one Philox block per four values, all four words used
+    q, e, m, _ = quantize(vals, bits, "packed", _lib.LQ_ROUND_PHILOX_LAYERED4, seed=2**40 + 7, layer=3, step=11)
+    u = oracle.words_to_uniform(oracle.layered4_words(2**40 + 7, 3, 11, vals.shape))
+    qo, eo, mo = oracle.mx_encode(vals, mmax, "stochastic", u)
+    assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(m, mo)
     # 64-bit reference counters (RNG_OFFSET >= 2**32 keeps both words, below it wraps to 32 bits)
     for off in (2**32 - 1000, 2**32 + 12345, 2**31 - 5):
         q, e, m, _ = quantize(vals[:64], bits, "packed", _lib.LQ_ROUND_PHILOX_REF, seed=1234, rng_offset=off)
@@ -320,6 +325,7 @@ def test_dense_fast_path_equals_general_kernel(bits, layout):
     rng = np.random.default_rng(32)
     words = t(rng.integers(0, 2**32, size=(b, h, p, n), dtype=np.uint64).astype(np.uint32).view(np.int32))
     for kw in (dict(stochastic=False), dict(stochastic=True, seed=5, rng_stream="reference"), dict(stochastic=True, seed=5),
+               dict(stochastic=True, seed=5, rng_stream="layered4"),
                dict(rand_words=words, rng_stream="reference"), dict(rand_words=words, rng_stream="layered")):
         res = []
         for use_dump in (False, True):
@@ -334,3 +340,26 @@ def test_dense_fast_path_equals_general_kernel(bits, layout):
             assert torch.equal(ya, yb), kw
         assert torch.equal(c_fast.q_state, c_gen.q_state) and torch.equal(c_fast.shared_exp, c_gen.shared_exp), kw
         assert torch.equal(c_fast.micro_exp, c_gen.micro_exp), kw
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_fused_update_layered4_stream(bits):
+    """LQ_ROUND_PHILOX_LAYERED4 inside the fused update: the codes are the reference's rounding rule applied to the
+    kernel's own fp32 state with the words of the (seed, layer, step, quad) keyed stream; two steps, so the step term
+    of the key is exercised."""
+    m = mk()
+    mmax = 63 if bits == 8 else 7
+    d = make_update_case(41, 2, 8, 64, 128, 2)
+    cache = m.allocate_state_kernel_cache(t(d["state"]), 16, bits)
+    cache.layer = 9
+    x, dt, A, B, C, D, z, bias = expand_update_operands(d)
+    for step in range(2):
+        h_out = torch.empty(d["state"].shape, dtype=torch.float32, device=dev())
+        m.mx_state_selective_update(cache, x, dt, A, B, C, D=D, dt_bias=bias, dt_softplus=True, stochastic=True, seed=77,
+                                    rng_stream="layered4", h_out=h_out)
+        torch.cuda.synchronize()
+        h = h_out.cpu().numpy()
+        u = oracle.words_to_uniform(oracle.layered4_words(77, 9, step, h.shape))
+        qo, eo, mo = oracle.mx_encode(h, mmax, "stochastic", u)
+        q, e, mi = cache_to_numpy(cache)
+        assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(mi, mo), step
