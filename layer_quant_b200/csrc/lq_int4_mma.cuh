@@ -649,13 +649,23 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
     if (lane == 0) s_den[r] = den;
   }
   __syncthreads();
-  for (int o = threadIdx.x; o < R * kD; o += kThreadsM) {
-    const int r = o / kD, d = o - r * kD;
-    const float* acc = p.part_acc + (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits * kD + d;
-    float O = 0.0f;
+  // four outputs per thread: the splits' partial results arrive as independent 128-bit loads, eight in flight per thread
+  for (int o = threadIdx.x; o < R * (kD / 4); o += kThreadsM) {
+    const int r = o / (kD / 4), d = (o - r * (kD / 4)) * 4;
+    const float4* acc = reinterpret_cast<const float4*>(p.part_acc + (static_cast<int64_t>(b) * a.q_heads + hq0 + r) * p.splits * kD + d);
+    float4 O = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
-    for (int s = 0; s < p.splits; ++s) O = fmaf(__ldcg(acc + static_cast<int64_t>(s) * kD), s_f[r * kMaxSplitsM + s], O);
-    store_from_float(a.out, b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2], a.dtype, O / s_den[r]);
+    for (int s = 0; s < p.splits; ++s) {
+      const float4 v = __ldcg(acc + static_cast<int64_t>(s) * (kD / 4));
+      const float f = s_f[r * kMaxSplitsM + s];
+      O.x = fmaf(v.x, f, O.x); O.y = fmaf(v.y, f, O.y); O.z = fmaf(v.z, f, O.z); O.w = fmaf(v.w, f, O.w);
+    }
+    const float den = s_den[r];
+    const int64_t ob = b * a.out_stride[0] + (hq0 + r) * a.out_stride[1] + d * a.out_stride[2];
+    store_from_float(a.out, ob, a.dtype, O.x / den);
+    store_from_float(a.out, ob + a.out_stride[2], a.dtype, O.y / den);
+    store_from_float(a.out, ob + 2 * a.out_stride[2], a.dtype, O.z / den);
+    store_from_float(a.out, ob + 3 * a.out_stride[2], a.dtype, O.w / den);
   }
   if (threadIdx.x == 0) p.counters[b * c.kv_heads + kvh] = 0;  // ready for the next launch
 }
