@@ -347,9 +347,11 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   const int n_rows = n_units * rows_per_pass;
   const uint64_t bh_first = u0 / units_per_head;                 // first (batch * heads + head) index touched
   const int n_heads = static_cast<int>((u1 - 1) / units_per_head - bh_first) + 1;
-  float* sx = smem_xy;        // x, later y, of the slab's rows
+  float* sx = smem_xy;        // x of the slab's rows
+  // read-out of the slab's rows: one partial sum per 16-value block when a row spans eight lanes (added up when
+  // the slab's y is written, in the order a butterfly over the eight lanes would add them), else the row's sum
   float* sy = sx + n_rows;
-  float* sdt = sy + n_rows;   // per touched head
+  float* sdt = sy + n_rows * (NBLK_T == 8 ? 8 : 1);   // per touched head
   float* sdA = sdt + n_heads;
 
   // (batch, head, row) of the slab's first row, once per CTA; rows inside the slab then need only
@@ -430,13 +432,11 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
       IO::store_ptr(qptr, eptr, mptr, codes, e_new, mic_new);
 
       if (NBLK_T == 8) {
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+        sy[row * 8 + blk] = y;
       } else {
         for (int o = nblk >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xFFFFFFFFu, y, o);
+        if (blk == 0) sy[row] = y;
       }
-      if (blk == 0) sy[row] = y;
       cur = nxt;
       qptr = qn; eptr = en; mptr = mn;
       lin += dl;
@@ -462,7 +462,13 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
     int b, h, p;
     row_coords(i, b, h, p);
-    float y = sy[i];
+    float y;
+    if (NBLK_T == 8) {
+      const float4 p0 = *reinterpret_cast<const float4*>(sy + i * 8), p1 = *reinterpret_cast<const float4*>(sy + i * 8 + 4);
+      y = ((p0.x + p1.x) + (p0.z + p1.z)) + ((p0.y + p1.y) + (p0.w + p1.w));  // the butterfly's order
+    } else {
+      y = sy[i];
+    }
     if (a.D) y += sx[i] * load_as_float(a.D, h * a.D_stride[0] + p * a.D_stride[1], a.D_dtype);
     if (a.z) y *= load_as_float(a.z, b * a.z_stride[0] + h * a.z_stride[1] + p * a.z_stride[2], a.z_dtype);
     store_from_float(a.out, b * a.out_stride[0] + h * a.out_stride[1] + p * a.out_stride[2], a.out_dtype, y);
@@ -598,9 +604,10 @@ template <int BITS, int LAYOUT>
 static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived& d, cudaStream_t st) {
   if (fast_update_applies<BITS, LAYOUT>(a, d)) {
     // One wave of resident CTAs (4 per SM) when a CTA's slab stays within kMaxUnitsPerCta units
-    // (its x / y staging in shared memory); more waves of equally sized slabs otherwise.
+    // (its x / y staging in shared memory: 36 bytes per row, 36 KB per CTA at most); more waves of equally sized
+    // slabs otherwise.
     uint64_t kMaxUnitsPerCta = 64;
-    if (const char* env = getenv("LQ_MX_MAX_UNITS")) kMaxUnitsPerCta = std::max(1, atoi(env));  // tuning aid
+    if (const char* env = getenv("LQ_MX_MAX_UNITS")) kMaxUnitsPerCta = std::min(80, std::max(1, atoi(env)));  // tuning aid; 80 units stay under 48 KB
     const int rows_per_pass = (32 >> d.lpr_log2) * (kUpdateThreads / 32);
     MxUpdateDerived dd = d;
     dd.units_total = static_cast<uint64_t>(a.state.batch) * a.state.heads * (a.state.dim / rows_per_pass);
@@ -613,7 +620,7 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
     const uint64_t max_units = (dd.units_total + ctas - 1) / ctas;
     const uint64_t max_heads = max_units / (a.state.dim / rows_per_pass) + 2;
     const dim3 grid(static_cast<unsigned>(ctas)), block(kUpdateThreads);
-    const size_t smem = sizeof(float) * (2 * max_units * rows_per_pass + 2 * max_heads);
+    const size_t smem = sizeof(float) * ((d.nblk == 8 ? 9 : 2) * max_units * rows_per_pass + 2 * max_heads);
     const MxUpdateDerived& d = dd;
     // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
     // running (its CTAs take the slots the predecessor's CTAs leave); it touches no global memory before its
