@@ -641,6 +641,32 @@ def main() -> int:
                                                   "us_per_launch": round(s / (5 * reps) * 1e6, 1)}
             del caches
             torch.cuda.empty_cache()
+        # Yardstick for short launches: a plain device-to-device copy (library code, not the product) moving the same
+        # number of bytes (read + written) as one launch of the cells above, replayed from a CUDA graph over buffers
+        # that rotate through more than 4x L2.  The HBM peak in the roofline is a long copy; a launch of 19 MB or 151 MB
+        # does not reach it whatever the kernel, and these cells say how far such a launch can get.
+        for label, total in (("19MB_config1_launch", MX8_BYTES_PER_SEQ_LAYER * 8), ("151MB", attn_bytes(16, 8192)),
+                             ("302MB", attn_bytes(8, 32768)), ("1208MB", attn_bytes(64, 16384))):
+            words = (total // 2 + 15) // 16 * 4  # int32 words per buffer; one launch reads and writes this much
+            reps = min(64, max(2, int(np.ceil(4 * 126e6 / total))))
+            srcs = [torch.empty(words, dtype=torch.int32, device=dev).random_(0, 1 << 20, generator=gen) for _ in range(reps)]
+            dsts = [torch.empty(words, dtype=torch.int32, device=dev) for _ in range(reps)]
+            entry = {"bytes_read_plus_written": 8 * words}
+            # "memcpy": cudaMemcpyAsync between device buffers; "elementwise": torch's vectorised add-one kernel on the SMs
+            for kind, op in (("memcpy", lambda d_, s_: d_.copy_(s_)), ("elementwise", lambda d_, s_: torch.add(s_, 1, out=d_))):
+                op(dsts[0], srcs[0])
+                torch.cuda.synchronize(dev)
+                copy_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(copy_graph):
+                    for s_, d_ in zip(srcs, dsts):
+                        op(d_, s_)
+                s = timed(copy_graph.replay, 5, 3)
+                gbs = 8 * words * reps * 5 / s / 1e9
+                entry[kind] = {"GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4), "us_per_launch": round(s / (5 * reps) * 1e6, 1)}
+                del copy_graph
+            sweep[f"copy_yardstick_{label}"] = entry
+            del srcs, dsts
+            torch.cuda.empty_cache()
         # prefill over the quantised cache (the step before decode): a 1024-token prompt, 8 sequences, one layer,
         # beside torch's fused attention over the un-quantised bf16 K / V (what the forward uses by default)
         import torch.nn.functional as F
