@@ -712,10 +712,11 @@ def main() -> int:
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle.timing as ot
-        csec, cores, nbytes, cdraw = ot.time_mx_update(B, 8, threads=os.cpu_count() or 1, repeats=3)
+        csec, cores, nbytes, cdraw = ot.time_mx_update(B, 8, threads=os.cpu_count() or 1, repeats=3, layers=LAYERS)
         cpu = {"value": nbytes / csec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-               "sample": f"one layer of the step (batch {B}, {nbytes / 1e6:.1f} MB algorithmic), numpy restatement of the reference "
+               "sample": f"the whole 24-layer step (batch {B}, {nbytes / 1e6:.1f} MB algorithmic), numpy restatement of the reference "
                          f"kernel (NOT the reference's own code), best of 3 runs, {cores} threads over (sequence, group) pieces",
+               "seconds_per_step": csec,
                "philox_draw_share": cdraw / csec}
 
     # ---- benchmark configuration 4 at every N: the full decode step of the 8B-shaped model ---------------------------

@@ -39,10 +39,10 @@ def make_config1_inputs(batch: int, seed: int = 0, heads: int = 128, dim: int = 
 
 
 def time_mx_update(batch: int = 8, format_bits: int = 8, threads: int | None = None, repeats: int = 1, seed: int = 0,
-                   heads: int = 128):
-    """Seconds per one-layer state update of ``batch`` sequences x ``heads`` heads (stochastic rounding,
-    reference Philox stream), best of ``repeats``.  The work is cut into (sequence, B/C group) pieces
-    dealt round-robin to ``threads`` workers, so every worker has work whenever batch x groups >= threads.
+                   heads: int = 128, layers: int = 1):
+    """Seconds per state update of ``layers`` layers (the same one-layer problem done ``layers`` times) of ``batch``
+    sequences x ``heads`` heads (stochastic rounding, reference Philox stream), best of ``repeats``.  The work is
+    cut into (sequence, B/C group) pieces dealt round-robin to ``threads`` workers, so every worker has work whenever batch x groups >= threads.
     Returns (seconds, threads that had work, algorithmic bytes, seconds of that spent drawing the
     Philox numbers): the draw is part of the reference kernel, so it is inside the timed region; it is
     reported separately because numpy evaluates Philox far less efficiently than the update."""
@@ -60,7 +60,7 @@ def time_mx_update(batch: int = 8, format_bits: int = 8, threads: int | None = N
     from .philox import tl_rand
 
     def work(w):
-        for bi, g in pieces[w::threads]:
+        for bi, g in pieces[w::threads] * layers:
             h0, h1 = g * hpg, (g + 1) * hpg
             # the counters the full-batch kernel gives these rows (:197-198)
             t0 = time.perf_counter()
@@ -84,4 +84,4 @@ def time_mx_update(batch: int = 8, format_bits: int = 8, threads: int | None = N
             sec = time.perf_counter() - t0
             if sec < best:
                 best, best_draw = sec, max(draw_seconds)
-    return best, threads, per_seq * batch, best_draw
+    return best, threads, per_seq * batch * layers, best_draw
