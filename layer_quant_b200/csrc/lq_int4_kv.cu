@@ -632,16 +632,30 @@ static int pick_splits(int batch, int kv_heads, int ctx_len) {
   return best;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device and process instead of on every launch (the
+// attribute belongs to the function on a device; each expansion site has its own record, one bit per device).
+#define LQ_SET_SMEM_ONCE(KERNEL_, BYTES_)                                                                          \
+  do {                                                                                                              \
+    static std::atomic<unsigned long long> lq_done_{0ull};                                                          \
+    int lq_dev_ = 0;                                                                                                \
+    LQ_CHECK_CUDA(cudaGetDevice(&lq_dev_));                                                                         \
+    const unsigned long long lq_bit_ = 1ull << (lq_dev_ & 63);                                                      \
+    if (lq_dev_ > 63 || !(lq_done_.load(std::memory_order_acquire) & lq_bit_)) {                                    \
+      LQ_CHECK_CUDA(cudaFuncSetAttribute(KERNEL_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES_)));     \
+      lq_done_.fetch_or(lq_bit_, std::memory_order_release);                                                        \
+    }                                                                                                               \
+  } while (0)
+
 template <int R, int GS>
 static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   using L = StageLayout<GS>;
   const size_t smem = kStages * L::kBytes + L::kNewRowBytes;
   const dim3 grid(p.splits, p.a.cache.kv_heads, p.a.cache.batch), block(kDecodeThreads);
   if (p.a.mask) {
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(int4_decode_kernel<R, GS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LQ_SET_SMEM_ONCE((int4_decode_kernel<R, GS, true>), smem);
     int4_decode_kernel<R, GS, true><<<grid, block, smem, st>>>(p);
   } else {
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(int4_decode_kernel<R, GS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LQ_SET_SMEM_ONCE((int4_decode_kernel<R, GS, false>), smem);
     int4_decode_kernel<R, GS, false><<<grid, block, smem, st>>>(p);
   }
   LQ_CHECK_CUDA(cudaGetLastError());
@@ -655,8 +669,7 @@ static int launch_decode_mma(const DecodeParams& p, cudaStream_t st) {
   const dim3 grid(p.splits, p.a.cache.kv_heads, p.a.cache.batch), block(mma::kThreadsM);
 #define LQ_MMA_LAUNCH(MASK_, SPLIT_)                                                                                \
   do {                                                                                                              \
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_>,                           \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                    \
+    LQ_SET_SMEM_ONCE((mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_>), smem);                                    \
     mma::int4_decode_mma_kernel<R, GS, MASK_, SPLIT_><<<grid, block, smem, st>>>(p);                                \
   } while (0)
   const bool qsplit = p.a.dtype != LQ_BF16;
@@ -824,8 +837,7 @@ static int launch_prefill_mma(const DecodeParams& p, cudaStream_t st) {
   const dim3 grid(static_cast<unsigned>(p.a.cache.batch) * p.nqb, p.a.cache.kv_heads, 1), block(mma::kThreadsM);
 #define LQ_PREFILL_LAUNCH(SPLIT_)                                                                                   \
   do {                                                                                                              \
-    LQ_CHECK_CUDA(cudaFuncSetAttribute(mma::int4_decode_mma_kernel<R, GS, false, SPLIT_, QB>,                       \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                    \
+    LQ_SET_SMEM_ONCE((mma::int4_decode_mma_kernel<R, GS, false, SPLIT_, QB>), smem);                                \
     mma::int4_decode_mma_kernel<R, GS, false, SPLIT_, QB><<<grid, block, smem, st>>>(p);                            \
   } while (0)
   if (p.a.dtype != LQ_BF16) LQ_PREFILL_LAUNCH(true); else LQ_PREFILL_LAUNCH(false);
