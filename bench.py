@@ -504,9 +504,9 @@ def main() -> int:
         return mk.mx_state_selective_update(cache, o["x"], o["dt"], o["A"], o["B"], o["C"], D=o["D"], dt_bias=o["dt_bias"],
                                             dt_softplus=True, stochastic=True, seed=0, rng_stream=args.rng, out=o["out"])
 
-    # The step's operands travel in E2E_CHUNKS pieces (6 layers each), and each piece's outputs leave as soon as its
-    # launches are done (in the recorded forms on a copy stream and a third stream, overlapping the compute).
-    E2E_CHUNKS = 4
+    # The step's operands travel in E2E_CHUNKS pieces, and each piece's outputs leave as soon as its launches are done (in
+    # the recorded forms on a copy stream and a third stream, overlapping the compute).
+    E2E_CHUNKS = int(os.environ.get("LQ_BENCH_E2E_CHUNKS", "4"))  # tuning aid; must divide the 24 layers
     lpc = LAYERS // E2E_CHUNKS
 
     def e2e_per_call_step():
@@ -557,10 +557,10 @@ def main() -> int:
     g_prepared = e2e_graph_of(lambda li: e2e_plans[li].run(), lambda: mk.advance_step_counter(counter))
     sec_e2e_prepared = timed(g_prepared.replay, args.steps, args.warmup)
     del g_prepared
-    # graph mode of the public call: each cache's step moves to a device counter the call advances on the stream
-    for cache, _ in e2e_layers:
-        cache.step_counter = torch.full((1,), int(cache.step), dtype=torch.int64, device=dev)
-        cache.step = 0
+    # graph mode of the public call, set up as for a model: the caches share one device counter, which the last layer's
+    # call advances on the stream
+    from types import SimpleNamespace
+    mk.prepare_graph_decode(SimpleNamespace(_mamba_decode_state_kernel_caches={id(c): c for c, _ in e2e_layers}))
     g_calls = e2e_graph_of(lambda li: call_layer(*e2e_layers[li]), lambda: None)
     e2e_step = g_calls.replay
     sec_e2e = timed(e2e_step, args.steps, args.warmup)
@@ -744,12 +744,13 @@ def main() -> int:
             "dtype": "f32", "data": "synthetic", "config": workload_config(world, B, args.rng),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3,
-                    "mode": "mx_state_selective_update (the reference's call signature) once per layer, caches in graph mode; pinned-host "
-                            "-> device copies of the step's x/dt/B/C in 4 pieces of 6 layers on a copy stream, device -> pinned-host "
-                            "copies of each piece's y on a third stream; calls and copies recorded once in a CUDA graph, replayed per step",
+                    "mode": "mx_state_selective_update (the reference's call signature) once per layer, caches in graph mode (one shared "
+                            f"device step counter); pinned-host -> device copies of the step's x/dt/B/C in {E2E_CHUNKS} pieces of {lpc} layers on a "
+                            "copy stream, device -> pinned-host copies of each piece's y on a third stream; calls and copies recorded once "
+                            "in a CUDA graph, replayed per step",
                     "per_call": {"value": bytes_step * world * args.steps / sec_e2e_call / 1e9,
                                  "ms_per_step": sec_e2e_call / args.steps * 1e3,
-                                 "mode": "the same 24 calls launched eagerly every step (no graph), copies in four pieces on the launching stream"},
+                                 "mode": f"the same 24 calls launched eagerly every step (no graph), copies in {E2E_CHUNKS} pieces on the launching stream"},
                     "prepared": {"value": bytes_step * world * args.steps / sec_e2e_prepared / 1e9,
                                  "ms_per_step": sec_e2e_prepared / args.steps * 1e3,
                                  "mode": "the graph built from prepared launches (MxUpdatePlan) sharing one step counter"}},

@@ -77,6 +77,9 @@ class MambaStateKernelCache:
     # Not in the reference: the step count kept on the device (one int64) once prepare_graph_decode has
     # run; the kernel adds it to ``step`` when it runs, so a recorded launch draws fresh numbers on replay.
     step_counter: torch.Tensor | None = None
+    # Whether this cache's update advances ``step_counter`` afterwards.  When the caches of one model share a counter
+    # (prepare_graph_decode), only the last layer's update does, once per decode step.
+    advances_counter: bool = True
     # Not in the reference: the argument block prepared by the last mx_state_selective_update call on this cache
     # and the operand signature it was prepared for.
     _plan: object = field(default=None, repr=False, compare=False)
@@ -370,7 +373,7 @@ def mx_state_selective_update(
             raise ValueError(f"Expected out shape {tuple(x.shape)}, got {tuple(out.shape)}")
         plan.rebind_out(out)
     y = plan.run()
-    if cache.step_counter is not None:
+    if cache.step_counter is not None and cache.advances_counter:
         advance_step_counter(cache.step_counter)
     return y
 
@@ -380,20 +383,37 @@ def _sig(t):
     return None if t is None else (t.data_ptr(), t.stride(), t.dtype)
 
 
-def prepare_graph_decode(model) -> None:
+def prepare_graph_decode(model, shared: bool = True) -> None:
     """Make the state updates of the registered caches replayable from a CUDA graph (not in the
-    reference, whose launch bakes the step in as a compile-time constant, :659): each cache's step
-    moves into a device counter that the kernel reads when it runs and that is advanced on the stream
-    after every update.  ``graph_decode_steps`` reads the counters back."""
-    for cache in getattr(model, "_mamba_decode_state_kernel_caches", {}).values():
-        if cache.step_counter is None:
-            cache.step_counter = torch.full((1,), int(cache.step), dtype=torch.int64, device=cache.q_state.device)
-            cache.step = 0  # the kernel uses step + counter
+    reference, whose launch bakes the step in as a compile-time constant, :659): the step count moves
+    into a device counter that the kernel reads when it runs (it uses ``cache.step + counter``) and that
+    is advanced on the stream.  ``graph_decode_steps`` reads the counters back.
+
+    ``shared`` (default): the caches on one device share ONE counter, advanced once per decode step by
+    the update of the highest-numbered layer, the last one a forward pass reaches, so a step costs one
+    counter bump instead of one per layer.  This is for loops that run every registered layer once per
+    step in layer order, which is what a model forward does; a loop that updates caches in another order,
+    or only some of them, passes ``shared=False`` and every cache gets and advances its own counter."""
+    caches = [c for c in getattr(model, "_mamba_decode_state_kernel_caches", {}).values() if c.step_counter is None]
+    if not shared:
+        for cache in caches:
+            cache.step_counter = torch.zeros((1,), dtype=torch.int64, device=cache.q_state.device)
+            cache.advances_counter = True
+        return
+    by_device: dict = {}
+    for cache in caches:
+        by_device.setdefault(cache.q_state.device, []).append(cache)
+    for device, group in by_device.items():
+        counter = torch.zeros((1,), dtype=torch.int64, device=device)
+        last = max(group, key=lambda c: c.layer)
+        for cache in group:
+            cache.step_counter = counter
+            cache.advances_counter = cache is last
 
 
 def graph_decode_steps(model) -> dict[int, int]:
-    """{layer: steps taken so far} read back from the device counters of the caches in graph mode."""
-    return {cache.layer: int(cache.step_counter.item())
+    """{layer: steps taken so far} of the caches in graph mode: the host-side step plus the device counter."""
+    return {cache.layer: int(cache.step) + int(cache.step_counter.item())
             for cache in getattr(model, "_mamba_decode_state_kernel_caches", {}).values() if cache.step_counter is not None}
 
 

@@ -363,3 +363,52 @@ def test_fused_update_layered4_stream(bits):
         qo, eo, mo = oracle.mx_encode(h, mmax, "stochastic", u)
         q, e, mi = cache_to_numpy(cache)
         assert np.array_equal(q, qo) and np.array_equal(e, eo) and np.array_equal(mi, mo), step
+
+
+@pytest.mark.parametrize("shared", [True, False])
+def test_graph_mode_step_counters_match_host_steps(shared):
+    """prepare_graph_decode moves the step count to the device: with one counter shared by a model's caches (advanced by
+    the last layer's update only) or one counter per cache, three decode steps over three layers leave exactly the
+    states, outputs and step counts that the same calls leave with the step kept on the host."""
+    from types import SimpleNamespace
+    m = mk()
+    gen = torch.Generator(device=dev()).manual_seed(5)
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return torch.randn(shape, generator=gen, device=dev(), dtype=torch.float32).to(dtype)
+
+    b, h, p, n, g = 2, 8, 64, 128, 2
+    states = [rand(b, h, p, n, dtype=torch.float32) * 0.5 for _ in range(3)]
+    ops = [dict(x=rand(b, h, p), dt=rand(b, h)[:, :, None].expand(b, h, p), A=-torch.rand(h, generator=gen, device=dev())[:, None, None].expand(h, p, n),
+                B=rand(b, g, n), C=rand(b, g, n)) for _ in range(3)]
+
+    def run(graph_mode):
+        caches = []
+        for li, st in enumerate(states):
+            c = m.allocate_state_kernel_cache(st, 16, 8)
+            c.layer = 10 * li + 3
+            c.step = 2  # as if two steps had been taken before
+            caches.append(c)
+        model = SimpleNamespace(_mamba_decode_state_kernel_caches={id(c): c for c in caches})
+        if graph_mode:
+            m.prepare_graph_decode(model, shared=shared)
+            if shared:
+                assert len({c.step_counter.data_ptr() for c in caches}) == 1
+                assert [c.advances_counter for c in caches] == [False, False, True]
+            else:
+                assert len({c.step_counter.data_ptr() for c in caches}) == 3 and all(c.advances_counter for c in caches)
+        ys = []
+        for _ in range(3):
+            for c, o in zip(caches, ops):
+                ys.append(m.mx_state_selective_update(c, o["x"], o["dt"], o["A"], o["B"], o["C"], dt_softplus=True, stochastic=True, seed=7).clone())
+        torch.cuda.synchronize()
+        steps = m.graph_decode_steps(model) if graph_mode else {c.layer: c.step for c in caches}
+        return caches, ys, steps
+
+    want_c, want_y, want_steps = run(False)
+    got_c, got_y, got_steps = run(True)
+    assert want_steps == got_steps == {3: 5, 13: 5, 23: 5}
+    for a, bb in zip(want_y, got_y):
+        assert torch.equal(a, bb)
+    for a, bb in zip(want_c, got_c):
+        assert torch.equal(a.q_state, bb.q_state) and torch.equal(a.shared_exp, bb.shared_exp) and torch.equal(a.micro_exp, bb.micro_exp)
