@@ -285,13 +285,18 @@ class MxUpdatePlan:
             r.step_counter = step_counter.data_ptr()
         self._fn = _lib.lib().lq_mx_state_update
         self._ref = ct.byref(a)
+        self._out_sig = (self.out.data_ptr(), self.out.stride(), self.out.dtype)
 
     def rebind_out(self, out: torch.Tensor) -> None:
         """Point the prepared call at another output tensor (shape and dtype of ``x``)."""
+        sig = (out.data_ptr(), out.stride(), out.dtype)
         self.out = out
+        if sig == self._out_sig:
+            return
+        self._out_sig = sig
         a = self.args
-        a.out = out.data_ptr()
-        a.out_stride[0], a.out_stride[1], a.out_stride[2] = out.stride()
+        a.out = sig[0]
+        a.out_stride[0], a.out_stride[1], a.out_stride[2] = sig[1]
         a.out_dtype = _lib.dtype_code(out)
 
     def run(self) -> torch.Tensor:
@@ -299,7 +304,7 @@ class MxUpdatePlan:
         step = int(self.cache.step)
         r.step = step
         r.rng_offset = (step * self.numel) & 0xFFFFFFFFFFFFFFFF
-        rc = self._fn(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
+        rc = self._fn(self._ref, _lib.stream_ptr(self.device))
         if rc:
             _lib.check(rc)
         if not r.step_counter:
