@@ -198,7 +198,7 @@ __device__ __forceinline__ float mx_update_readout16(float (&hv)[16], const floa
 // mantissa of 2^15 (value 32768 + 128 + q), then ONE exact FMA per value: (32896 + q) * s - 32896 * s.
 // The per-pair scale is built on the FMA pipe from the micro bit: bits(s) = e << 23 + micro << 23.
 __device__ __forceinline__ void mx_decode_block(const uint32_t (&codes)[4], uint32_t e, uint32_t micro_bits, float (&h)[16]) {
-  if (e >= 1u && e <= 229u) {
+  if (__all_sync(__activemask(), e - 1u <= 228u)) {  // one uniform branch per warp; the exact path below takes every e
     const uint32_t ebits = e << 23;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {

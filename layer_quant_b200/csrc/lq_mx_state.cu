@@ -371,10 +371,13 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   uint8_t* qptr = static_cast<uint8_t*>(s.q_state) + (R0 + r_first) * q_row + blk * IO::kQBytes;
   uint8_t* eptr = s.shared_exp + (R0 + r_first) * e_row + blk;
   uint8_t* mptr = s.micro_exp + (R0 + r_first) * m_row + blk * IO::kMicroBytes;
-  uint64_t lin = (R0 + r_first) * dstate + n0;
+  // linear index of the block's first value, kept pre-shifted to the Philox counter in the layered modes (block index /
+  // quad index), so that the loop carries the counter itself
+  constexpr int kCtrShift = MODE == LQ_ROUND_PHILOX_LAYERED ? 4 : (MODE == LQ_ROUND_PHILOX_LAYERED4 ? 2 : 0);
+  uint64_t lin = ((R0 + r_first) * dstate + n0) >> kCtrShift;
   uint32_t row = r_first;
   const uint32_t dq = rows_per_pass * q_row, de = rows_per_pass * e_row, dm = rows_per_pass * m_row,
-                 dl = rows_per_pass * dstate;
+                 dl = (rows_per_pass * dstate) >> kCtrShift;
   // everything above is arithmetic on the arguments; from here on memory the predecessor may have written is read
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // the first row's block travels while the operands below are staged
@@ -426,7 +429,8 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
       mx_decode_block(codes, cur.e, cur.mic, hv);
       float y = mx_update_readout16(hv, Bv, Cv, dA_h, dt_h, sx[row]);  // h' = h exp(A dt) + (B dt) x
 
-      const MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin);
+      MxRoundCtx ctx = round_ctx_at<MODE>(rb, lin << kCtrShift);
+      if (kCtrShift) ctx.counter = lin;
       uint32_t e_new, mic_new;
       mx_encode_block<BITS, MODE>(hv, cut, ctx, d.keys, codes, e_new, mic_new);
       IO::store_ptr(qptr, eptr, mptr, codes, e_new, mic_new);
