@@ -400,11 +400,12 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   // position of the first unit: head index inside the slab, unit inside the head, head inside its group
   int head_i = 0;
   int unit_in_head = static_cast<int>(u0 % units_per_head);
-  int h_cur = h_first;
   int b_cur = b_first;
+  int g_cur = h_first / heads_per_group;                 // B / C group of the current head ...
+  int h_in_group = h_first - g_cur * heads_per_group;    // ... and the head's place in it: advanced without divisions
   float Bv[16], Cv[16];
-  load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, h_cur / heads_per_group, n0, Bv);
-  load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
+  load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, g_cur, n0, Bv);
+  load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, g_cur, n0, Cv);
   const MxRoundBase rb = make_round_base(a.rounding, static_cast<uint64_t>(s.batch) * H * P * dstate);
 
   __syncthreads();
@@ -449,16 +450,14 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
     // the next unit, if any, starts another head; B / C change only with the (batch, group)
     unit_in_head = 0;
     ++head_i;
-    if (u < n_units) {
-      const int g_old = h_cur / heads_per_group;
-      if (++h_cur == H) {
-        h_cur = 0;
+    if (u < n_units && ++h_in_group == heads_per_group) {
+      h_in_group = 0;
+      if (++g_cur == a.ngroups) {
+        g_cur = 0;
         ++b_cur;
       }
-      if (h_cur / heads_per_group != g_old || h_cur == 0) {
-        load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, h_cur / heads_per_group, n0, Bv);
-        load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, h_cur / heads_per_group, n0, Cv);
-      }
+      load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, g_cur, n0, Bv);
+      load_bc16(a.C, a.C_stride, a.C_dtype, b_cur, g_cur, n0, Cv);
     }
   }
   __syncthreads();
