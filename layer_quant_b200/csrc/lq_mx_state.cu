@@ -20,6 +20,10 @@
 namespace lq {
 
 constexpr int kUpdateThreads = 128;
+// the slab kernel runs two warps per CTA, eight CTAs per SM: the same sixteen warps per SM as four CTAs of four warps
+// (the register file allows no more), cut into slabs half as large
+constexpr int kFastThreads = 64;
+constexpr int kFastCtasPerSm = 8;
 
 // ---- block load / store in either storage layout -----------------------------------------------
 struct MxRaw {
@@ -309,7 +313,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
 // on the host): dense state tensors, dt / dt_bias / A per head only, dstate / 16 a power of two,
 // dim a multiple of the rows one CTA pass covers, no h_out.
 //
-// Work is cut into units of `rows_per_pass` consecutive rows (one pass of the CTA's four warps).
+// Work is cut into units of `rows_per_pass` consecutive rows (one pass of the CTA's two warps).
 // Units are numbered in memory order, so CTA c owns units [c U / G, (c + 1) U / G): a contiguous
 // slab of the state, balanced to within one unit whatever the batch, and the grid is one wave of
 // resident CTAs whenever the slab's x / y staging fits in shared memory.  Every lane is always
@@ -318,7 +322,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
 // NBLK_T = dstate / 16 when known at compile time (8 for Nemotron-H: all lane and address arithmetic
 // folds to constants and the read-out reduction unrolls), 0 = taken from the arguments.
 template <int BITS, int LAYOUT, int MODE, int NBLK_T>
-__global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
+__global__ void __launch_bounds__(kFastThreads, kFastCtasPerSm) mx_state_update_fast_kernel(const lq_mx_update_args a, const MxUpdateDerived d) {
   using IO = MxBlockIO<BITS, LAYOUT>;
   extern __shared__ float smem_xy[];
   const lq_mx_state& s = a.state;
@@ -330,7 +334,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   const int blk = lane & (nblk - 1);
   const int rsub = lane >> lpr_log2;
   const int rows_per_warp = 32 >> lpr_log2;
-  const int rows_per_pass = rows_per_warp * (kUpdateThreads / 32);
+  const int rows_per_pass = rows_per_warp * (kFastThreads / 32);
   const int units_per_head = P / rows_per_pass;
   const int heads_per_group = H / a.ngroups;
   const int n0 = blk * 16;
@@ -383,12 +387,12 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   // the first row's block travels while the operands below are staged
   MxRaw cur = IO::load_ptr(qptr, eptr, mptr);
 
-  for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
+  for (int i = threadIdx.x; i < n_rows; i += kFastThreads) {
     int b, h, p;
     row_coords(i, b, h, p);
     sx[i] = load_as_float(a.x, b * a.x_stride[0] + h * a.x_stride[1] + p * a.x_stride[2], a.x_dtype);
   }
-  for (int i = threadIdx.x; i < n_heads; i += kUpdateThreads) {
+  for (int i = threadIdx.x; i < n_heads; i += kFastThreads) {
     const unsigned hh = static_cast<unsigned>(h_first + i);
     const int h = static_cast<int>(hh % static_cast<unsigned>(H)), b = b_first + static_cast<int>(hh / static_cast<unsigned>(H));
     float dt = load_as_float(a.dt, b * a.dt_stride[0] + h * a.dt_stride[1], a.dt_dtype);
@@ -462,7 +466,7 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_fast_kernel
   }
   __syncthreads();
   // y = <h', C> + D x (* z), stored for the whole slab at once
-  for (int i = threadIdx.x; i < n_rows; i += kUpdateThreads) {
+  for (int i = threadIdx.x; i < n_rows; i += kFastThreads) {
     int b, h, p;
     row_coords(i, b, h, p);
     float y;
@@ -594,7 +598,7 @@ static bool fast_update_applies(const lq_mx_update_args& a, const MxUpdateDerive
   using IO = MxBlockIO<BITS, LAYOUT>;
   const lq_mx_state& s = a.state;
   const int64_t q_row = static_cast<int64_t>(d.nblk) * IO::kQBytes, m_row = static_cast<int64_t>(d.nblk) * IO::kMicroBytes;
-  const int rows_per_pass = (32 >> d.lpr_log2) * (kUpdateThreads / 32);
+  const int rows_per_pass = (32 >> d.lpr_log2) * (kFastThreads / 32);
   const bool dense = s.q_stride[2] == q_row && s.q_stride[1] == q_row * s.dim && s.q_stride[0] == q_row * s.dim * s.heads &&
                      s.exp_stride[2] == d.nblk && s.exp_stride[1] == static_cast<int64_t>(d.nblk) * s.dim &&
                      s.exp_stride[0] == static_cast<int64_t>(d.nblk) * s.dim * s.heads && s.micro_stride[2] == m_row &&
@@ -606,15 +610,15 @@ static bool fast_update_applies(const lq_mx_update_args& a, const MxUpdateDerive
 template <int BITS, int LAYOUT>
 static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived& d, cudaStream_t st) {
   if (fast_update_applies<BITS, LAYOUT>(a, d)) {
-    // One wave of resident CTAs (4 per SM) when a CTA's slab stays within kMaxUnitsPerCta units
-    // (its x / y staging in shared memory: 36 bytes per row, 36 KB per CTA at most); more waves of equally sized
+    // One wave of resident CTAs (8 per SM) when a CTA's slab stays within kMaxUnitsPerCta units
+    // (its x / y staging in shared memory: 36 bytes per row, 18 KB per CTA at most); more waves of equally sized
     // slabs otherwise.
     uint64_t kMaxUnitsPerCta = 64;
     if (const char* env = getenv("LQ_MX_MAX_UNITS")) kMaxUnitsPerCta = std::min(80, std::max(1, atoi(env)));  // tuning aid; 80 units stay under 48 KB
-    const int rows_per_pass = (32 >> d.lpr_log2) * (kUpdateThreads / 32);
+    const int rows_per_pass = (32 >> d.lpr_log2) * (kFastThreads / 32);
     MxUpdateDerived dd = d;
     dd.units_total = static_cast<uint64_t>(a.state.batch) * a.state.heads * (a.state.dim / rows_per_pass);
-    const uint64_t wave = 4ull * sm_count();
+    const uint64_t wave = static_cast<uint64_t>(kFastCtasPerSm) * sm_count();
     uint64_t ctas = std::min<uint64_t>(dd.units_total, wave);
     if (dd.units_total > ctas * kMaxUnitsPerCta) {
       ctas = (dd.units_total + kMaxUnitsPerCta - 1) / kMaxUnitsPerCta;
@@ -622,7 +626,7 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
     }
     const uint64_t max_units = (dd.units_total + ctas - 1) / ctas;
     const uint64_t max_heads = max_units / (a.state.dim / rows_per_pass) + 2;
-    const dim3 grid(static_cast<unsigned>(ctas)), block(kUpdateThreads);
+    const dim3 grid(static_cast<unsigned>(ctas)), block(kFastThreads);
     const size_t smem = sizeof(float) * ((d.nblk == 8 ? 9 : 2) * max_units * rows_per_pass + 2 * max_heads);
     const MxUpdateDerived& d = dd;
     // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
