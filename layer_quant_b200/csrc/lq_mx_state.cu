@@ -165,8 +165,14 @@ struct MxUpdateDerived {
   int32_t a_scalar;    // A depends on the head only
   int32_t heads_per_cta;  // consecutive heads of one B/C group handled by one CTA
   PhiloxKeys keys;        // round keys of rounding.seed
-  uint64_t units_total;   // fast path: batch * heads * dim / rows per pass
+  uint64_t units_total;   // fast path: batch * heads * dim / rows per pass (< 2^31)
+  // fast path: the slab of a CTA without a division.  units_per_cta / units_rem: CTA c owns units_per_cta units, the
+  // first units_rem CTAs one more.  FastDiv: floor(n / d) for n < 2^31 as (mulhi(n, magic) + n) >> shift.
+  uint32_t units_per_cta, units_rem;
+  struct FastDiv { uint32_t magic, shift; } div_units_per_head, div_heads, div_dim, div_heads_per_group;
 };
+
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const MxUpdateDerived::FastDiv& f) { return (__umulhi(n, f.magic) + n) >> f.shift; }
 
 // One CTA = `hpc` consecutive heads of one (batch, B/C group): B and C are fetched once and stay in
 // registers for hpc * dim rows.  gridDim.x = batch * (heads / hpc).
@@ -311,10 +317,11 @@ __global__ void __launch_bounds__(kUpdateThreads, 4) mx_state_update_kernel(cons
 
 // Fast path of the fused update: the shape every Mamba2 decode step has.  Requirements (checked
 // on the host): dense state tensors, dt / dt_bias / A per head only, dstate / 16 a power of two,
-// dim a multiple of the rows one CTA pass covers, no h_out.
+// dim a multiple of the rows one CTA pass covers, no h_out, fewer than 2^31 units.
 //
 // Work is cut into units of `rows_per_pass` consecutive rows (one pass of the CTA's two warps).
-// Units are numbered in memory order, so CTA c owns units [c U / G, (c + 1) U / G): a contiguous
+// Units are numbered in memory order and dealt out contiguously, U / G to each of the G CTAs and one
+// more to the first U mod G: a contiguous
 // slab of the state, balanced to within one unit whatever the batch, and the grid is one wave of
 // resident CTAs whenever the slab's x / y staging fits in shared memory.  Every lane is always
 // active, the three state pointers move by a constant per pass (also across head boundaries), and
@@ -340,17 +347,18 @@ __global__ void __launch_bounds__(kFastThreads, kFastCtasPerSm) mx_state_update_
   const int n0 = blk * 16;
   const unsigned int* cut = mx_exp_cut_table<BITS>();
 
-  // this CTA's slab: units [u0, u1), rows [R0, R1) of the [batch * heads * dim] row space
-  const uint64_t u0 = static_cast<uint64_t>(blockIdx.x) * d.units_total / gridDim.x;
-  const uint64_t u1 = static_cast<uint64_t>(blockIdx.x + 1) * d.units_total / gridDim.x;
-  const int n_units = static_cast<int>(u1 - u0);
+  // this CTA's slab: units [u0, u1), rows [R0, R1) of the [batch * heads * dim] row space; the first units_rem CTAs
+  // take one unit more than the others
+  const uint32_t u0 = blockIdx.x * d.units_per_cta + min(blockIdx.x, d.units_rem);
+  const int n_units = static_cast<int>(d.units_per_cta + (blockIdx.x < d.units_rem ? 1u : 0u));
+  const uint32_t u1 = u0 + n_units;
   // let the next kernel in the stream be scheduled behind this one (no effect without the launch attribute)
   asm volatile("griddepcontrol.launch_dependents;");
   if (n_units == 0) return;
-  const uint64_t R0 = u0 * rows_per_pass;
+  const uint64_t R0 = static_cast<uint64_t>(u0) * rows_per_pass;
   const int n_rows = n_units * rows_per_pass;
-  const uint64_t bh_first = u0 / units_per_head;                 // first (batch * heads + head) index touched
-  const int n_heads = static_cast<int>((u1 - 1) / units_per_head - bh_first) + 1;
+  const uint32_t bh_first = fast_div(u0, d.div_units_per_head);  // first (batch * heads + head) index touched
+  const int n_heads = static_cast<int>(fast_div(u1 - 1, d.div_units_per_head) - bh_first) + 1;
   float* sx = smem_xy;        // x of the slab's rows
   // read-out of the slab's rows: one partial sum per 16-value block when a row spans eight lanes (added up when
   // the slab's y is written, in the order a butterfly over the eight lanes would add them), else the row's sum
@@ -358,16 +366,19 @@ __global__ void __launch_bounds__(kFastThreads, kFastCtasPerSm) mx_state_update_
   float* sdt = sy + n_rows * (NBLK_T == 8 ? 8 : 1);   // per touched head
   float* sdA = sdt + n_heads;
 
-  // (batch, head, row) of the slab's first row, once per CTA; rows inside the slab then need only
-  // 32-bit arithmetic
-  const int p_first = static_cast<int>(R0 % P);
-  const int h_first = static_cast<int>(bh_first % H), b_first = static_cast<int>(bh_first / H);
+  // (batch, head, row) of the slab's first row, once per CTA
+  const int unit_in_head0 = static_cast<int>(u0 - bh_first * static_cast<uint32_t>(units_per_head));
+  const int p_first = unit_in_head0 * rows_per_pass;
+  const int b_first = static_cast<int>(fast_div(bh_first, d.div_heads));
+  const int h_first = static_cast<int>(bh_first - static_cast<uint32_t>(b_first) * static_cast<uint32_t>(H));
   auto row_coords = [&](int i, int& b, int& h, int& p) {
-    const unsigned pi = static_cast<unsigned>(p_first + i);
-    const unsigned hh = static_cast<unsigned>(h_first) + pi / static_cast<unsigned>(P);
-    p = static_cast<int>(pi % static_cast<unsigned>(P));
-    b = b_first + static_cast<int>(hh / static_cast<unsigned>(H));
-    h = static_cast<int>(hh % static_cast<unsigned>(H));
+    const uint32_t pi = static_cast<uint32_t>(p_first + i);
+    const uint32_t hq = fast_div(pi, d.div_dim);
+    p = static_cast<int>(pi - hq * static_cast<uint32_t>(P));
+    const uint32_t hh = static_cast<uint32_t>(h_first) + hq;
+    const uint32_t bq = fast_div(hh, d.div_heads);
+    b = b_first + static_cast<int>(bq);
+    h = static_cast<int>(hh - bq * static_cast<uint32_t>(H));
   };
   const uint32_t q_row = nblk * IO::kQBytes, m_row = nblk * IO::kMicroBytes, e_row = nblk;
   const uint32_t r_first = warp * rows_per_warp + rsub;
@@ -403,9 +414,9 @@ __global__ void __launch_bounds__(kFastThreads, kFastCtasPerSm) mx_state_update_
   }
   // position of the first unit: head index inside the slab, unit inside the head, head inside its group
   int head_i = 0;
-  int unit_in_head = static_cast<int>(u0 % units_per_head);
+  int unit_in_head = unit_in_head0;
   int b_cur = b_first;
-  int g_cur = h_first / heads_per_group;                 // B / C group of the current head ...
+  int g_cur = static_cast<int>(fast_div(static_cast<uint32_t>(h_first), d.div_heads_per_group));  // B / C group of the current head ...
   int h_in_group = h_first - g_cur * heads_per_group;    // ... and the head's place in it: advanced without divisions
   float Bv[16], Cv[16];
   load_bc16(a.B, a.B_stride, a.B_dtype, b_cur, g_cur, n0, Bv);
@@ -603,8 +614,10 @@ static bool fast_update_applies(const lq_mx_update_args& a, const MxUpdateDerive
                      s.exp_stride[2] == d.nblk && s.exp_stride[1] == static_cast<int64_t>(d.nblk) * s.dim &&
                      s.exp_stride[0] == static_cast<int64_t>(d.nblk) * s.dim * s.heads && s.micro_stride[2] == m_row &&
                      s.micro_stride[1] == m_row * s.dim && s.micro_stride[0] == m_row * s.dim * s.heads;
+  // fewer than 2^31 units keep the kernel's index arithmetic in 32 bits and its multiply-high divisions exact
+  const uint64_t units = static_cast<uint64_t>(s.batch) * s.heads * (s.dim / rows_per_pass);
   return dense && d.dt_uniform && d.a_scalar && a.h_out == nullptr && (1 << d.lpr_log2) == d.nblk &&
-         s.dim % rows_per_pass == 0;
+         s.dim % rows_per_pass == 0 && units < (1ull << 31);
 }
 
 template <int BITS, int LAYOUT>
@@ -624,6 +637,19 @@ static void launch_update_mode(const lq_mx_update_args& a, const MxUpdateDerived
       ctas = (dd.units_total + kMaxUnitsPerCta - 1) / kMaxUnitsPerCta;
       ctas = (ctas + wave - 1) / wave * wave;
     }
+    dd.units_per_cta = static_cast<uint32_t>(dd.units_total / ctas);
+    dd.units_rem = static_cast<uint32_t>(dd.units_total % ctas);
+    auto fast_div_of = [](uint32_t dv) {
+      MxUpdateDerived::FastDiv f;
+      f.shift = 0;
+      while ((1ull << f.shift) < dv) ++f.shift;  // ceil(log2 dv)
+      f.magic = static_cast<uint32_t>(((1ull << (32 + f.shift)) + dv - 1) / dv - (1ull << 32));
+      return f;
+    };
+    dd.div_units_per_head = fast_div_of(static_cast<uint32_t>(a.state.dim / rows_per_pass));
+    dd.div_heads = fast_div_of(static_cast<uint32_t>(a.state.heads));
+    dd.div_dim = fast_div_of(static_cast<uint32_t>(a.state.dim));
+    dd.div_heads_per_group = fast_div_of(static_cast<uint32_t>(a.state.heads / a.ngroups));
     const uint64_t max_units = (dd.units_total + ctas - 1) / ctas;
     const uint64_t max_heads = max_units / (a.state.dim / rows_per_pass) + 2;
     const dim3 grid(static_cast<unsigned>(ctas)), block(kFastThreads);
