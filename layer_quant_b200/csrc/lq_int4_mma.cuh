@@ -263,22 +263,39 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
   float qoff[4], qoff_lo[QSPLIT ? 4 : 1];
   auto bf_lo = [](uint32_t v) { return __uint_as_float(v << 16); };
   auto bf_hi = [](uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); };
+  // this lane's query row; a bf16 query whose head dims are contiguous and 16-byte aligned arrives as one 128-bit load per
+  // chunk (the lane's eight dims 32 i + 8 t .. + 7), anything else as scalar loads
+  const bool q_row_valid = hrow < RV && (!PREFILL || q_first + hrow / R < p.q_len);
+  const int64_t q_row_base = b * a.q_stride[0] + (kvh * R + hrow % R) * a.q_stride[1] +
+                             (PREFILL ? (q_first + hrow / R) * p.q_stride_t : 0);
+  const bool q_vec = !QSPLIT && a.dtype == LQ_BF16 && a.q_stride[2] == 1 &&
+                     ((reinterpret_cast<uintptr_t>(a.q) | (static_cast<uint64_t>(a.q_stride[0]) * 2) |
+                       (static_cast<uint64_t>(a.q_stride[1]) * 2) | (PREFILL ? static_cast<uint64_t>(p.q_stride_t) * 2 : 0)) & 15) == 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float qs = 0.0f, qs_lo = 0.0f;
+    uint4 qw = make_uint4(0u, 0u, 0u, 0u);  // dims 8t .. 8t+7 of chunk i as bf16 pairs (vector path)
+    if (q_vec && q_row_valid)
+      qw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.q) + q_row_base + 32 * i + 8 * t));
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       const int d0 = 32 * i + 8 * t + 2 * s;
+      uint32_t pa, pb;
       float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-      if (hrow < RV && (!PREFILL || q_first + hrow / R < p.q_len)) {
-        const int64_t qb = b * a.q_stride[0] + (kvh * R + hrow % R) * a.q_stride[1] +
-                           (PREFILL ? (q_first + hrow / R) * p.q_stride_t : 0);
-        q0 = load_as_float(a.q, qb + (d0 + 0) * a.q_stride[2], a.dtype);
-        q1 = load_as_float(a.q, qb + (d0 + 4) * a.q_stride[2], a.dtype);
-        q2 = load_as_float(a.q, qb + (d0 + 1) * a.q_stride[2], a.dtype);
-        q3 = load_as_float(a.q, qb + (d0 + 5) * a.q_stride[2], a.dtype);
+      if (q_vec) {  // (dim d0, d0 + 4) and (d0 + 1, d0 + 5) out of the eight loaded values
+        const uint32_t wl = s == 0 ? qw.x : qw.y, wh = s == 0 ? qw.z : qw.w;
+        pa = __byte_perm(wl, wh, 0x5410);
+        pb = __byte_perm(wl, wh, 0x7632);
+      } else {
+        if (q_row_valid) {
+          q0 = load_as_float(a.q, q_row_base + (d0 + 0) * a.q_stride[2], a.dtype);
+          q1 = load_as_float(a.q, q_row_base + (d0 + 4) * a.q_stride[2], a.dtype);
+          q2 = load_as_float(a.q, q_row_base + (d0 + 1) * a.q_stride[2], a.dtype);
+          q3 = load_as_float(a.q, q_row_base + (d0 + 5) * a.q_stride[2], a.dtype);
+        }
+        pa = pack_bf16x2(q0, q1);
+        pb = pack_bf16x2(q2, q3);
       }
-      const uint32_t pa = pack_bf16x2(q0, q1), pb = pack_bf16x2(q2, q3);
       qa[i][s][0] = pa;  // a0: row g, k = 2t, 2t+1
       qa[i][s][1] = pb;  // a2: row g, k = 2t+8, 2t+9
       qs += (bf_lo(pa) + bf_hi(pa)) + (bf_lo(pb) + bf_hi(pb));  // of the values the fragments hold
