@@ -43,6 +43,9 @@ __device__ __forceinline__ uint32_t s2u(const void* p) { return static_cast<uint
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -215,23 +218,37 @@ __global__ void __launch_bounds__(kThreadsM, (R * (QB > 0 ? QB : 1) <= 4 && !QSP
   const uint8_t* const v_rows = c.v_packed + vp_base;
   const uint8_t* const scale_rows = reinterpret_cast<const uint8_t*>(scale_which ? c.v_scale + vs_base : c.k_scale + ks_base);
   const uint32_t smem_base = s2u(smem);
+  // Tiles are issued in order, so a full tile costs five copies from running pointers; the last, partial tile of the
+  // context takes the general form with per-row byte counts (rows past the end are zero-filled).
+  const uint8_t* k_src = k_rows + static_cast<int64_t>(tile_begin) * (kTileTok * 64) + code_src_off;
+  const uint8_t* v_src = v_rows + static_cast<int64_t>(tile_begin) * (kTileTok * 64) + code_src_off;
+  const uint8_t* s_src = scale_rows + static_cast<int64_t>(tile_begin) * (kTileTok * G * 4) + scale_off;
   auto issue_tile = [&](int it) {
     const uint32_t stage = smem_base + (it % kStagesM) * L::kStage;
     const int tok0 = (tile_begin + it) * kTileTok;
-    const int rows = min(kTileTok, rl.ctx_len - tok0);
-    const int64_t tile_off = static_cast<int64_t>(tok0) * 64;
-    const uint32_t ok0 = static_cast<int>(r0) < rows ? 16u : 0u, ok1 = static_cast<int>(r0) + 32 < rows ? 16u : 0u;
-    const int64_t o0 = tile_off + (ok0 ? code_src_off : 0), o1 = tile_off + (ok1 ? code_src_off + 2048 : 0);
-    cp_async16(stage + L::kKc + code_dst_off, k_rows + o0, ok0);
-    cp_async16(stage + L::kKc + code_dst_off + 2048, k_rows + o1, ok1);
-    cp_async16(stage + L::kVc + code_dst_off, v_rows + o0, ok0);
-    cp_async16(stage + L::kVc + code_dst_off + 2048, v_rows + o1, ok1);
-    if (has_scale_chunk) {
-      const int left = rows * G * 4 - scale_off;
-      const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? static_cast<uint32_t>(left) : 0u);
-      cp_async16(stage + (scale_which ? L::kVs : L::kKs) + scale_off,
-                 scale_rows + static_cast<int64_t>(tok0) * (G * 4) + (nbytes ? scale_off : 0), nbytes);
+    if (tok0 + kTileTok <= rl.ctx_len) {
+      cp_async16_full(stage + L::kKc + code_dst_off, k_src);
+      cp_async16_full(stage + L::kKc + code_dst_off + 2048, k_src + 2048);
+      cp_async16_full(stage + L::kVc + code_dst_off, v_src);
+      cp_async16_full(stage + L::kVc + code_dst_off + 2048, v_src + 2048);
+      if (has_scale_chunk) cp_async16_full(stage + (scale_which ? L::kVs : L::kKs) + scale_off, s_src);
+    } else {
+      const int rows = rl.ctx_len - tok0;
+      const uint32_t ok0 = static_cast<int>(r0) < rows ? 16u : 0u, ok1 = static_cast<int>(r0) + 32 < rows ? 16u : 0u;
+      const int64_t back = -static_cast<int64_t>(code_src_off);  // rows past the end copy nothing, from the tile's first byte
+      cp_async16(stage + L::kKc + code_dst_off, k_src + (ok0 ? 0 : back), ok0);
+      cp_async16(stage + L::kKc + code_dst_off + 2048, k_src + (ok1 ? 2048 : back), ok1);
+      cp_async16(stage + L::kVc + code_dst_off, v_src + (ok0 ? 0 : back), ok0);
+      cp_async16(stage + L::kVc + code_dst_off + 2048, v_src + (ok1 ? 2048 : back), ok1);
+      if (has_scale_chunk) {
+        const int left = rows * G * 4 - scale_off;
+        const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? static_cast<uint32_t>(left) : 0u);
+        cp_async16(stage + (scale_which ? L::kVs : L::kKs) + scale_off, s_src - (nbytes ? 0 : scale_off), nbytes);
+      }
     }
+    k_src += kTileTok * 64;
+    v_src += kTileTok * 64;
+    s_src += kTileTok * G * 4;
   };
 
   // start the ring now: the first tiles travel while the new row is quantised and the Q fragments are built
