@@ -315,11 +315,14 @@ def test_errors_match_reference_behaviour():
 
 
 @pytest.mark.parametrize("bits,layout", [(8, "packed"), (8, "reference"), (4, "packed"), (4, "reference")])
-def test_dense_fast_path_equals_general_kernel(bits, layout):
+@pytest.mark.parametrize("shape", [(3, 16, 64, 128, 2), (40, 12, 40, 128, 3)])
+def test_dense_fast_path_equals_general_kernel(bits, layout, shape):
     """The dense fast-path kernel (taken when no fp32 state dump is requested and the shape is the
-    regular decode shape) and the general kernel must agree bit for bit, in every rounding mode."""
+    regular decode shape) and the general kernel must agree bit for bit, in every rounding mode.  The second
+    shape has heads, rows per head and heads per group that are not powers of two and enough rows that a CTA's
+    slab crosses heads and sequences: the slab kernel finds its coordinates by multiply-high instead of division."""
     m = mk()
-    b, h, p, n, g = 3, 16, 64, 128, 2
+    b, h, p, n, g = shape
     d = make_update_case(31, b, h, p, n, g, with_z=True)
     x, dt, A, B, C, D, z, bias = expand_update_operands(d)
     rng = np.random.default_rng(32)
