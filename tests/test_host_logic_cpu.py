@@ -249,3 +249,39 @@ def test_dense_oracle_against_plain_torch():
     want = torch.nn.functional.conv1d(seq, T(w)[:, None], T(bc), groups=5)[:, :, -1]
     np.testing.assert_allclose(out, torch.nn.functional.silu(want).numpy(), rtol=1e-5, atol=1e-6)
     assert np.array_equal(win, seq[:, :, 1:].float().numpy())
+
+
+def test_prepare_graph_decode_counters_on_the_host():
+    """prepare_graph_decode's bookkeeping needs no GPU: caches of one model share one step counter, advanced by the
+    highest-numbered layer only; shared=False gives every cache a counter of its own; caches already in graph mode are
+    left alone; graph_decode_steps adds the host-side step to the counter."""
+    from types import SimpleNamespace
+    from hybrid_quant import mamba_state_8b_kernel as mk
+
+    def caches():
+        out = []
+        for layer, step in ((7, 3), (2, 3), (11, 3)):
+            c = mk.MambaStateKernelCache(torch.zeros(1, 2, 16, 128, dtype=torch.int8), torch.zeros(1, 2, 16, 8, dtype=torch.uint8),
+                                         torch.zeros(1, 2, 16, 64, dtype=torch.uint8), 8, step)
+            c.layer = layer
+            out.append(c)
+        return out
+
+    cs = caches()
+    model = SimpleNamespace(_mamba_decode_state_kernel_caches={id(c): c for c in cs})
+    mk.prepare_graph_decode(model)
+    assert len({c.step_counter.data_ptr() for c in cs}) == 1 and cs[0].step_counter.dtype == torch.int64
+    assert [c.advances_counter for c in cs] == [False, False, True]  # layer 11 is the last a forward pass reaches
+    assert [c.step for c in cs] == [3, 3, 3]
+    cs[0].step_counter += 4  # what four replayed decode steps leave behind
+    assert mk.graph_decode_steps(model) == {7: 7, 2: 7, 11: 7}
+    counter = cs[0].step_counter
+    mk.prepare_graph_decode(model)  # a second call changes nothing
+    assert all(c.step_counter is counter for c in cs)
+
+    cs = caches()
+    model = SimpleNamespace(_mamba_decode_state_kernel_caches={id(c): c for c in cs})
+    mk.prepare_graph_decode(model, shared=False)
+    assert len({c.step_counter.data_ptr() for c in cs}) == 3 and all(c.advances_counter for c in cs)
+    assert mk.graph_decode_steps(model) == {7: 3, 2: 3, 11: 3}
+    mk.prepare_graph_decode(SimpleNamespace())  # a model without registered caches: nothing to do
